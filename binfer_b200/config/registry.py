@@ -71,6 +71,8 @@ def _register_builtin() -> None:
     register_architecture("Gukidra", GukidraConfig.from_dict)
     from .fikotar import FikotarConfig
     register_architecture("Fikotar", FikotarConfig.from_dict)
+    from .ketopel import KetopelConfig
+    register_architecture("Ketopel", KetopelConfig.from_dict)
 
 
 _register_builtin()

@@ -26,6 +26,12 @@ class RopeSpec:
     factor: float = 1.0
     # scaling by wavelength: see WavelengthScaling; None = none
     wavelength_scaling: Optional["WavelengthScaling"] = None
+    # scaling by pair index with a ramp between two indices: see RampScaling; None = none
+    ramp_scaling: Optional["RampScaling"] = None
+    # "half": the pair (i, i + rot/2); "interleaved": the pair (2i, 2i + 1)
+    layout: str = "half"
+    # where in a head the rotated sizes start (0: the head's first ``rotary_dim`` sizes)
+    offset: int = 0
 
 
 @dataclass(frozen=True)
@@ -39,6 +45,23 @@ class WavelengthScaling:
     low: float = 1.0
     high: float = 4.0
     original: float = 8192.0
+
+
+@dataclass(frozen=True)
+class RampScaling:
+    """Frequencies stretched for contexts beyond ``original`` positions, by pair index.  A
+    wave that makes t turns over ``original`` positions has the (real-valued) index
+    ``n(t) = rot ln(original / (2 pi t)) / (2 ln theta)``.  With ``lo = max(floor(n(fast)),
+    0)``, ``hi = min(ceil(n(slow)), rot - 1)`` and ``r_i = clamp((i - lo) / max(hi - lo,
+    0.001), 0, 1)`` the frequency of pair i is ``(1 - r_i) f_i + r_i f_i / factor``: fast
+    waves stay, slow ones are divided by ``factor``.  Cosines and sines are multiplied by
+    ``magnitude`` (None: ``0.1 ln(factor) + 1``), which scales q and k alike."""
+
+    factor: float = 1.0
+    original: float = 4096.0
+    fast: float = 32.0
+    slow: float = 1.0
+    magnitude: Optional[float] = None
 
 
 @dataclass(frozen=True)
@@ -100,7 +123,7 @@ class GatedMLPSpec:
 
     kind: str = "gated_mlp"
     intermediate_size: int = 0
-    activation: str = "silu"
+    activation: str = "silu"     # or "gelu_tanh": 0.5 z (1 + tanh(sqrt(2/pi) (z + 0.044715 z^3)))
     bias: bool = False
     # the tensors' names inside the feed-forward's prefix: gate, up, down
     names: Tuple[str, str, str] = ("gate_proj.weight", "up_proj.weight", "down_proj.weight")
@@ -171,9 +194,12 @@ class ConvWindowAttentionSpec:
     """Grouped-query softmax attention whose q, k and v projections pass a short causal
     convolution over time, with a sliding window that keeps the request's first tokens.
 
-    Order: projection, convolution per channel (``conv_taps`` taps, 0 or 1: none), rotation of
-    q and k (``position``), each q and k head divided by its root mean square
-    (``unit_norm``, no weight, ``norm_eps``), scores ``(q . k) * scale``, the mask (position i
+    Order: projection, convolution per channel (``conv_taps`` taps, 0 or 1: none), an RMS norm
+    with weights over the whole q projection and over the whole k projection, all heads at
+    once (``proj_norm``; tensors ``q_norm``, ``k_norm`` of the projections' sizes; without a
+    convolution only), rotation of q and k (``position``), each q and k head divided by its
+    root mean square (``unit_norm``, no weight, ``norm_eps``), scores ``(q . k) * scale``, a
+    soft cap ``s <- c tanh(s / c)`` (``softcap`` c > 0), the mask (position i
     sees j <= i with ``i - j < window`` or ``j < keep_first``; ``window`` None: every j <= i),
     softmax whose denominator also holds ``exp(sink_h)`` when ``sinks``, values of size
     ``value_dim``, output projection.  ``names``: the tensors inside the mixer's prefix;
@@ -192,8 +218,11 @@ class ConvWindowAttentionSpec:
     window: Optional[int] = None
     keep_first: int = 0
     sinks: bool = False
+    proj_norm: bool = False
+    softcap: float = 0.0
     names: Tuple[Tuple[str, str], ...] = (("q", "q"), ("k", "k"), ("v", "v"), ("o", "o"),
-                                          ("sink", "sink"))
+                                          ("sink", "sink"), ("q_norm", "q.norm"),
+                                          ("k_norm", "k.norm"))
     conv_suffix: str = ".conv"
 
     @property
@@ -205,8 +234,13 @@ class ConvWindowAttentionSpec:
 class RetentionSpec:
     """Linear attention with a fixed decay per head: ``S <- decay_h S + k v^T``, ``o = S^T q``
     (no softmax, no denominator).  q and k are turned by ``position`` and k multiplied by
-    ``qk_dim ** -0.5``; each head's output is divided by its root mean square (``norm_eps``,
-    no weight), multiplied by ``silu`` of a gate projection and projected."""
+    ``k_scale`` (None: ``qk_dim ** -0.5``); each head's output is divided by its root mean
+    square (``norm_eps``, no weight), multiplied by ``silu`` of a gate projection and projected.
+
+    ``activation`` ("silu"): applied to the q, k and v projections first (lightning
+    attention).  ``norm_over`` "all": one root mean square over the concatenated heads
+    instead of one per head.  ``norm_weight``: the normed output is multiplied by a tensor
+    ``norm`` of ``heads * v_dim`` numbers.  ``gate``: "silu" or "sigmoid"."""
 
     kind: str = "retention"
     num_heads: int = 0
@@ -215,8 +249,72 @@ class RetentionSpec:
     decays: Tuple[float, ...] = ()
     position: Optional[RopeSpec] = None
     norm_eps: float = 1e-6
+    k_scale: Optional[float] = None
+    activation: Optional[str] = None
+    norm_over: str = "head"
+    norm_weight: bool = False
+    gate: str = "silu"
     names: Tuple[Tuple[str, str], ...] = (("q", "q"), ("k", "k"), ("v", "v"), ("g", "g"),
-                                          ("o", "o"))
+                                          ("o", "o"), ("norm", "norm"))
+
+
+@dataclass(frozen=True)
+class LatentAttentionSpec:
+    """Causal softmax attention whose keys and values are expanded from one cached latent
+    vector per token.  A down projection yields ``kv_rank + rot_dim`` numbers: the first
+    ``kv_rank``, RMS-normed with a weight, are the latent c; the last ``rot_dim``, rotated,
+    are a key part that all heads share.  Head h has the key ``[W_uk,h c | shared part]``
+    against a query ``[head_dim plain | rot_dim rotated]`` and the value ``W_uv,h c`` of
+    ``value_dim`` numbers.  Only c and the shared part are cached.  ``head_gate``: head h's
+    output is multiplied by the sigmoid of a projection of the mixer's input to one number
+    per head.  ``position``: the rotation of the ``rot_dim`` parts (layout and offset are
+    set by the mixer).  ``names``: the tensors inside the mixer's prefix."""
+
+    kind: str = "latent_attention"
+    num_heads: int = 0
+    head_dim: int = 0            # plain (unrotated) sizes of a query/key head
+    rot_dim: int = 0
+    value_dim: int = 0
+    kv_rank: int = 0
+    scale: Optional[float] = None    # None = 1/sqrt(head_dim + rot_dim)
+    norm_eps: float = 1e-6
+    position: Optional[RopeSpec] = None
+    head_gate: bool = True
+    names: Tuple[Tuple[str, str], ...] = (("q", "q"), ("dkv", "dkv"), ("dkv_norm", "dkv.norm"),
+                                          ("uk", "uk"), ("uv", "uv"), ("g", "g"), ("o", "o"))
+
+    @property
+    def softmax_scale(self) -> float:
+        return self.scale if self.scale is not None else (self.head_dim + self.rot_dim) ** -0.5
+
+
+@dataclass(frozen=True)
+class GatedDeltaRuleSpec:
+    """A matrix memory written by the delta rule with a decay per token and head.  Per value
+    head, with a state ``S [qk_dim, v_dim]`` that starts at zero::
+
+        S <- g S;   u = beta (v - S^T k);   S <- S + k u^T;   o = S^T q
+
+    q and k have ``num_qk_heads`` heads (value head h reads head ``h // (num_heads /
+    num_qk_heads)``); q, k and v pass a causal convolution of ``conv_taps`` taps per channel
+    and ``silu``; q and k are then made unit vectors per head (``x / sqrt(sum x^2 +
+    unit_eps)``) and q multiplied by ``qk_dim ** -0.5``.  ``beta = sigmoid(W_b h)`` and
+    ``g = exp(-exp(A_log) softplus(W_a h + dt_bias))``, one each per value head.  Each head's
+    output is divided by its root mean square (``norm_eps``), multiplied by a weight of
+    ``v_dim`` numbers that the heads share and by ``silu`` of a gate projection."""
+
+    kind: str = "gated_delta_rule"
+    num_heads: int = 0
+    num_qk_heads: int = 0
+    qk_dim: int = 0
+    v_dim: int = 0
+    conv_taps: int = 0
+    unit_eps: float = 1e-6
+    norm_eps: float = 1e-6
+    names: Tuple[Tuple[str, str], ...] = (
+        ("q", "q"), ("k", "k"), ("v", "v"), ("b", "b"), ("a", "a"), ("g", "g"), ("o", "o"),
+        ("A_log", "A_log"), ("dt_bias", "dt_bias"), ("norm", "norm"))
+    conv_suffix: str = ".conv"
 
 
 @dataclass(frozen=True)
@@ -274,16 +372,29 @@ class LayerSpec:
 
 
 @dataclass(frozen=True)
+class PassStart:
+    """What is added to the residual stream right before a schedule entry that opens a pass
+    over a run of layers that is walked several times: the embedding output once more
+    (``embedding``), then row ``row`` of the model's table of pass vectors
+    (:attr:`ModelSpec.pass_table`; None: nothing)."""
+
+    embedding: bool = False
+    row: Optional[int] = None
+
+
+@dataclass(frozen=True)
 class ScheduleEntry:
     """One execution of a layer.
 
     ``layer`` indexes :attr:`ModelSpec.layers`.  ``cache_from`` is ``None`` when
     this execution keeps a cache of its own, else the index of the schedule
-    entry whose cache it reads (it then writes none).
+    entry whose cache it reads (it then writes none).  ``before``: see
+    :class:`PassStart`.
     """
 
     layer: int
     cache_from: Optional[int] = None
+    before: Optional[PassStart] = None
 
 
 @dataclass(frozen=True)
@@ -304,6 +415,9 @@ class ModelSpec:
     logit_scale: float = 1.0
     # tensor-name layout of the family (prefixes for embed, layers, norm, head)
     names: "NameLayout" = None
+    # (tensor name, rows) of a table ``[rows, hidden_size]`` whose rows schedule entries add
+    # to the stream (ScheduleEntry.before); None: the model has none
+    pass_table: Optional[Tuple[str, int]] = None
 
 
 @dataclass(frozen=True)

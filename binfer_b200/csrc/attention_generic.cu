@@ -24,21 +24,26 @@
 // (`dv`), and a window that keeps the request's first tokens: with keep_first > 0 the keys
 // j < keep_first stay visible behind the window, at their true positions.  They are walked
 // first, again in tiles of 32 counted from position 0.  `out_stride` and `out_scale` let the
-// result land, scaled, in a column block of a wider buffer.
+// result land, scaled, in a column block of a wider buffer.  `v_stride` is the distance, in
+// elements, between the value rows of neighbouring tokens of a page: with v_cache = k_cache
+// and v_stride = d the values are the first dv numbers of the keys themselves (attention over
+// a latent vector per token that serves as key and as value).  Values up to 256 a head keep
+// 8 sums a lane, larger ones (up to 512) 16.
 #include <float.h>
 
 #include "common.cuh"
 
-#define ATT_MAX_ACC 8   // head_dim <= 32 * ATT_MAX_ACC
+#define ATT_MAX_D 1024  // keys: a query head in shared memory per warp
 
-template <typename A>
+template <typename A, int ATT_MAX_ACC>     // value size <= 32 * ATT_MAX_ACC
 __global__ void paged_attention_generic_kernel(
     const A* __restrict__ q, const A* __restrict__ k_cache, const A* __restrict__ v_cache,
     const int* __restrict__ seq_of_token, const int* __restrict__ positions,
     const int* __restrict__ block_tables, int table_stride, A* __restrict__ out, int nh, int nkv,
     int d, int page_size, int num_pages, int window, float scale, float softcap,
     const float* __restrict__ slopes, const float* __restrict__ sinks, int* __restrict__ err,
-    int dv, int keep_first, long long q_stride, long long out_stride, float out_scale) {
+    int dv, int keep_first, long long q_stride, long long out_stride, float out_scale,
+    long long v_stride) {
   extern __shared__ float sh[];
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
   const int warps = blockDim.x >> 5;
@@ -103,7 +108,7 @@ __global__ void paged_attention_generic_kernel(
       if (!((live >> jj) & 1u)) continue;
       const float pb = __shfl_sync(0xffffffffu, pj, jj);
       const long long rb = __shfl_sync(0xffffffffu, row, jj);
-      const A* vr = v_cache + rb * dv;
+      const A* vr = v_cache + rb * v_stride;
 #pragma unroll
       for (int c = 0; c < ATT_MAX_ACC; ++c) {
         const int i = lane + 32 * c;
@@ -132,22 +137,24 @@ BF_EXPORT int bf_paged_attention_generic(
     const int* positions, const int* block_tables, int table_stride, void* out, int T, int nh,
     int nkv, int d, int page_size, int num_pages, int window, float scale, float softcap,
     const float* slopes, const float* sinks, int act_dtype, int* err, int dv, int keep_first,
-    long long q_stride, long long out_stride, float out_scale, cudaStream_t stream) {
+    long long q_stride, long long out_stride, float out_scale, long long v_stride,
+    cudaStream_t stream) {
   if (T <= 0) return 0;
-  if (d > 32 * ATT_MAX_ACC || dv > 32 * ATT_MAX_ACC || nkv <= 0 || nh % nkv)
-    return (int)cudaErrorInvalidValue;
+  if (d > ATT_MAX_D || dv > 512 || nkv <= 0 || nh % nkv) return (int)cudaErrorInvalidValue;
+  if (v_stride <= 0) v_stride = dv;
   const int warps = 4;
   dim3 grid(T, (nh + warps - 1) / warps);
   const size_t smem = (size_t)warps * d * sizeof(float);
-  if (act_dtype == BF_DTYPE_F32)
-    paged_attention_generic_kernel<float><<<grid, warps * 32, smem, stream>>>(
-        (const float*)q, (const float*)k_cache, (const float*)v_cache, seq_of_token, positions,
-        block_tables, table_stride, (float*)out, nh, nkv, d, page_size, num_pages, window, scale,
-        softcap, slopes, sinks, err, dv, keep_first, q_stride, out_stride, out_scale);
-  else
-    paged_attention_generic_kernel<__nv_bfloat16><<<grid, warps * 32, smem, stream>>>(
-        (const __nv_bfloat16*)q, (const __nv_bfloat16*)k_cache, (const __nv_bfloat16*)v_cache,
-        seq_of_token, positions, block_tables, table_stride, (__nv_bfloat16*)out, nh, nkv, d,
-        page_size, num_pages, window, scale, softcap, slopes, sinks, err, dv, keep_first, q_stride, out_stride, out_scale);
+#define ATT_GO(AT, ACC)                                                                        \
+  paged_attention_generic_kernel<AT, ACC><<<grid, warps * 32, smem, stream>>>(                 \
+      (const AT*)q, (const AT*)k_cache, (const AT*)v_cache, seq_of_token, positions,           \
+      block_tables, table_stride, (AT*)out, nh, nkv, d, page_size, num_pages, window, scale,   \
+      softcap, slopes, sinks, err, dv, keep_first, q_stride, out_stride, out_scale, v_stride)
+  if (act_dtype == BF_DTYPE_F32) {
+    if (dv <= 256) ATT_GO(float, 8); else ATT_GO(float, 16);
+  } else {
+    if (dv <= 256) ATT_GO(__nv_bfloat16, 8); else ATT_GO(__nv_bfloat16, 16);
+  }
+#undef ATT_GO
   return bf_launch_status();
 }

@@ -2,7 +2,10 @@
 // a short causal convolution over time: convolution per channel, rotation of q and k, a
 // weightless RMS norm of each q and k head after the rotation, q to its buffer, k and v into
 // the cache pages.  Every step is optional (taps 0: no convolution, 1: a factor per channel
-// and no state; rot_half 0: no rotation; unit_norm 0: no norm).
+// and no state; rot_half 0: no rotation; unit_norm 0: no norm).  Between the convolution and
+// the rotation q and k may be multiplied by a factor per token (`pre_factor` [T][2]: q, k) and a
+// weight per channel (`pre_weight`): an RMS norm over a whole projection, whose factor a kernel
+// in front has taken.  The cosines and sines are multiplied by `rot_mag`.
 //
 //   y_t[c] = sum_j w[c, j] * u_{t - taps + 1 + j}[c],   j = 0 .. taps-1
 //
@@ -25,13 +28,13 @@
 // table [T][rot_half] of (cos, sin).
 __global__ void rope_table_kernel(const int* __restrict__ positions,
                                   const float* __restrict__ inv_freq, int T, int rot_half,
-                                  float2* __restrict__ table) {
+                                  float rot_mag, float2* __restrict__ table) {
   const int i = blockIdx.x * blockDim.x + threadIdx.x;
   if (i >= T * rot_half) return;
   const int t = i / rot_half, m = i - t * rot_half;
   float sn, cs;
   sincosf((float)positions[t] * inv_freq[m], &sn, &cs);
-  table[i] = make_float2(cs, sn);
+  table[i] = make_float2(cs * rot_mag, sn * rot_mag);
 }
 
 // two neighbouring values of the activation type
@@ -56,7 +59,8 @@ __global__ void conv_encode_kernel(
     const float2* __restrict__ rope, int rot_half, const int* __restrict__ slots,
     A* __restrict__ q_out, long long q_stride, A* __restrict__ k_cache, A* __restrict__ v_cache,
     int T, int nh, int nkv, int dk, int dv, int page_size, long long num_slots, int unit_norm,
-    float eps, int vec2, int hpw, int* __restrict__ err) {
+    float eps, int vec2, int hpw, int* __restrict__ err, const float* __restrict__ pre_factor,
+    const float* __restrict__ pre_weight) {
   extern __shared__ float sh[];
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
   const int heads_total = nh + 2 * nkv;
@@ -125,6 +129,11 @@ __global__ void conv_encode_kernel(
     }
   }
   __syncwarp();
+  if (pre_factor && kind < 2) {                // the norm over the whole projection
+    const float f = pre_factor[(size_t)t * 2 + kind];
+    for (int i = lane; i < d; i += 32) buf[i] *= f * pre_weight[c0 + i];
+    __syncwarp();
+  }
   float ss = 0.f;
   const bool turn = kind < 2 && rot_half > 0;
   const float2* cs_sn = rope + (size_t)t * rot_half;
@@ -168,16 +177,18 @@ BF_EXPORT int bf_conv_encode(
     const int* q_start, const float* inv_freq, int rot_half, const int* positions,
     const int* slots, void* q_out, long long q_stride, void* k_cache, void* v_cache, int T,
     int nh, int nkv, int dk, int dv, int page_size, long long num_slots, int unit_norm, float eps,
-    int act_dtype, float* rope_table, int* err, cudaStream_t stream) {
+    int act_dtype, float* rope_table, int* err, const float* pre_factor,
+    const float* pre_weight, float rot_mag, cudaStream_t stream) {
   // rope_table: scratch, float [T][rot_half][2] (unused without a rotation)
   if (T <= 0) return 0;
   if (taps > CE_MAX_TAPS || (taps > 1 && !state)) return (int)cudaErrorInvalidValue;
   if (taps < 1) conv_w = nullptr;              // (one tap: a factor per channel, no state)
+  if (!pre_factor || !pre_weight) pre_factor = pre_weight = nullptr;
   if (rot_half > 0) {
     if (!rope_table) return (int)cudaErrorInvalidValue;
     const int n = T * rot_half;
     rope_table_kernel<<<(n + 127) / 128, 128, 0, stream>>>(positions, inv_freq, T, rot_half,
-                                                          (float2*)rope_table);
+                                                          rot_mag, (float2*)rope_table);
     const int e = bf_launch_status();
     if (e) return e;
   }
@@ -199,13 +210,14 @@ BF_EXPORT int bf_conv_encode(
         (const float*)proj, stride, conv_w, taps, state, state_stride, state_slots, n_state_slots,
         seq_of_token, q_start, (const float2*)rope_table, rot_half, slots, (float*)q_out,
         q_stride, (float*)k_cache, (float*)v_cache, T, nh, nkv, dk, dv, page_size, num_slots,
-        unit_norm, eps, vec2, hpw, err);
+        unit_norm, eps, vec2, hpw, err, pre_factor, pre_weight);
   else
     conv_encode_kernel<__nv_bfloat16><<<blocks, warps * 32, smem, stream>>>(
         (const __nv_bfloat16*)proj, stride, conv_w, taps, state, state_stride, state_slots,
         n_state_slots, seq_of_token, q_start, (const float2*)rope_table, rot_half, slots,
         (__nv_bfloat16*)q_out, q_stride, (__nv_bfloat16*)k_cache, (__nv_bfloat16*)v_cache, T, nh,
-        nkv, dk, dv, page_size, num_slots, unit_norm, eps, vec2, hpw, err);
+        nkv, dk, dv, page_size, num_slots, unit_norm, eps, vec2, hpw, err, pre_factor,
+        pre_weight);
   return bf_launch_status();
 }
 

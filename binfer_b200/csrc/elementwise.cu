@@ -217,7 +217,17 @@ BF_EXPORT int bf_residual_add(float* resid, const void* delta, long long n, int 
 // out[t, c] = silu(gu[t, c]) * gu[t, I + c],  silu(g) = g / (1 + exp(-g))
 // (cuda/kernels/bf16_kernels.cu:461-477; there gate and up are separate buffers,
 // here they are the two halves of one fused projection's output row).
-template <typename A>
+// ACT 1: the tanh form of gelu in silu's place,
+//   gelu(g) = 0.5 g (1 + tanh(sqrt(2/pi) (g + 0.044715 g^3))).
+#define BF_ACT_SILU 0
+#define BF_ACT_GELU_TANH 1
+template <int ACT>
+__device__ __forceinline__ float bf_gate_act(float g) {
+  if (ACT == BF_ACT_GELU_TANH)
+    return 0.5f * g * (1.f + tanhf(0.7978845608028654f * (g + 0.044715f * g * g * g)));
+  return g / (1.f + expf(-g));
+}
+template <typename A, int ACT>
 __global__ void silu_mul_kernel(const A* __restrict__ gu, A* __restrict__ out, int T, int I) {
   const size_t n = (size_t)T * I;
   size_t i = (size_t)blockIdx.x * blockDim.x + threadIdx.x;
@@ -226,7 +236,7 @@ __global__ void silu_mul_kernel(const A* __restrict__ gu, A* __restrict__ out, i
     const size_t t = i / I, c = i - t * I;
     const float g = bf_ld(gu + t * 2 * I + c);
     const float u = bf_ld(gu + t * 2 * I + I + c);
-    bf_st(out + i, g / (1.f + expf(-g)) * u);
+    bf_st(out + i, bf_gate_act<ACT>(g) * u);
   }
 }
 
@@ -234,6 +244,15 @@ __global__ void silu_mul_kernel(const A* __restrict__ gu, A* __restrict__ out, i
 // approximations (relative error about 2^-21, far inside the bf16 result's 2^-9).  With the
 // accurate expf and division the bf16 kernel was bound by arithmetic, not by memory.
 __device__ __forceinline__ float bf_silu_fast(float g) { return __fdividef(g, 1.f + __expf(-g)); }
+// ... and gelu's tanh form the same way: 0.5 g (1 + tanh(z)) = g / (1 + exp(-2 z))
+template <int ACT>
+__device__ __forceinline__ float bf_gate_act_fast(float g) {
+  if (ACT == BF_ACT_GELU_TANH) {
+    const float z = 0.7978845608028654f * (g + 0.044715f * g * g * g);
+    return __fdividef(g, 1.f + __expf(-2.f * z));
+  }
+  return bf_silu_fast(g);
+}
 
 // The same when the rows of gu still lack a factor (see BfRowScale).  I is at least 256, so
 // the 32 chunks of a warp lie in at most two rows, whose factors the warp works out itself,
@@ -284,6 +303,7 @@ __global__ void silu_mul_bf16_scaled_kernel(const __nv_bfloat16* __restrict__ gu
 }
 
 // bf16, I a multiple of 8: eight elements per thread with 16-byte loads and stores.
+template <int ACT>
 __global__ void silu_mul_bf16_vec_kernel(const __nv_bfloat16* __restrict__ gu,
                                          __nv_bfloat16* __restrict__ out, int T, int I) {
   BF_TRACE_POINT(10 * BF_TR_SILU);
@@ -315,7 +335,7 @@ __global__ void silu_mul_bf16_vec_kernel(const __nv_bfloat16* __restrict__ gu,
 #pragma unroll
       for (int j = 0; j < 4; ++j) {
         const float2 g = __bfloat1622float2(g2[j]), u = __bfloat1622float2(u2[j]);
-        o2[j] = __floats2bfloat162_rn(bf_silu_fast(g.x) * u.x, bf_silu_fast(g.y) * u.y);
+        o2[j] = __floats2bfloat162_rn(bf_gate_act_fast<ACT>(g.x) * u.x, bf_gate_act_fast<ACT>(g.y) * u.y);
       }
       *reinterpret_cast<uint4*>(out + (k ? t2 * I + c2 : t * I + c)) = o4;
     }
@@ -339,26 +359,41 @@ BF_EXPORT int bf_silu_mul_scaled(const void* gu, void* out, int T, int I,
                        (const __nv_bfloat16*)gu, (__nv_bfloat16*)out, T, I, rs);
 }
 
-BF_EXPORT int bf_silu_mul(const void* gu, void* out, int T, int I, int act_dtype,
-                          cudaStream_t stream) {
+template <int ACT>
+static int gated_act_mul_launch(const void* gu, void* out, int T, int I, int act_dtype,
+                                cudaStream_t stream) {
   if (T <= 0) return 0;
   const int threads = 256;
   if (act_dtype == BF_DTYPE_BF16 && I % 8 == 0 && ((uintptr_t)gu & 15) == 0 &&
       ((uintptr_t)out & 15) == 0) {
     long long blocks = ((long long)T * (I / 8) + threads - 1) / threads;
     if (blocks > 148 * 16) blocks = 148 * 16;
-    return bf_launch_pdl(silu_mul_bf16_vec_kernel, dim3((int)blocks), dim3(threads), 0, stream,
-                         (const __nv_bfloat16*)gu, (__nv_bfloat16*)out, T, I);
+    return bf_launch_pdl(silu_mul_bf16_vec_kernel<ACT>, dim3((int)blocks), dim3(threads), 0,
+                         stream, (const __nv_bfloat16*)gu, (__nv_bfloat16*)out, T, I);
   }
   long long blocks = ((long long)T * I + threads - 1) / threads;
   if (blocks > 148 * 32) blocks = 148 * 32;
   if (act_dtype == BF_DTYPE_F32)
-    silu_mul_kernel<float><<<(int)blocks, threads, 0, stream>>>((const float*)gu, (float*)out,
-                                                               T, I);
+    silu_mul_kernel<float, ACT><<<(int)blocks, threads, 0, stream>>>((const float*)gu,
+                                                                    (float*)out, T, I);
   else
-    silu_mul_kernel<__nv_bfloat16><<<(int)blocks, threads, 0, stream>>>(
+    silu_mul_kernel<__nv_bfloat16, ACT><<<(int)blocks, threads, 0, stream>>>(
         (const __nv_bfloat16*)gu, (__nv_bfloat16*)out, T, I);
   return bf_launch_status();
+}
+
+BF_EXPORT int bf_silu_mul(const void* gu, void* out, int T, int I, int act_dtype,
+                          cudaStream_t stream) {
+  return gated_act_mul_launch<BF_ACT_SILU>(gu, out, T, I, act_dtype, stream);
+}
+
+// out[t, c] = act(gu[t, c]) * gu[t, I + c] with act 0: silu, 1: gelu's tanh form.
+BF_EXPORT int bf_gated_act_mul(const void* gu, void* out, int T, int I, int act, int act_dtype,
+                               cudaStream_t stream) {
+  if (act == BF_ACT_SILU) return gated_act_mul_launch<BF_ACT_SILU>(gu, out, T, I, act_dtype, stream);
+  if (act == BF_ACT_GELU_TANH)
+    return gated_act_mul_launch<BF_ACT_GELU_TANH>(gu, out, T, I, act_dtype, stream);
+  return (int)cudaErrorInvalidValue;
 }
 
 // ------------------------------------------------------------- token ids from the device

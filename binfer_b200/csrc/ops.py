@@ -182,6 +182,21 @@ def silu_mul(gate_up: torch.Tensor, out: torch.Tensor,
                              _c_int(_dtype_code(out)), _stream())
 
 
+GATE_ACTIVATIONS = {"silu": 0, "gelu_tanh": 1}
+
+
+def gated_act_mul(gate_up: torch.Tensor, out: torch.Tensor, activation: str) -> None:
+    """out[t, c] = act(gate_up[t, c]) * gate_up[t, I + c]; ``activation`` one of
+    ``GATE_ACTIVATIONS``."""
+    T, I = out.shape
+    if activation not in GATE_ACTIVATIONS:
+        raise KernelError(f"gated_act_mul: unknown activation {activation!r}")
+    if gate_up.shape != (T, 2 * I) or not gate_up.is_contiguous() or gate_up.dtype != out.dtype:
+        raise KernelError("gated_act_mul: gate_up must be contiguous [T, 2*I] of the output's dtype")
+    _run("gated_act_mul", lib().bf_gated_act_mul, _ptr(gate_up), _ptr(out), _c_int(T), _c_int(I),
+         _c_int(GATE_ACTIVATIONS[activation]), _c_int(_dtype_code(out)), _stream())
+
+
 def copy_ids(dst: torch.Tensor, src: torch.Tensor, pairs: torch.Tensor, n: int) -> None:
     """dst[pairs[i, 0]] = src[pairs[i, 1]] for i < n (int32 everywhere)."""
     _want(dst, torch.int32, "dst"); _want(src, torch.int32, "src"); _want(pairs, torch.int32, "pairs")
@@ -222,18 +237,22 @@ def paged_attention_generic(q: torch.Tensor, k_cache: torch.Tensor, v_cache: tor
                             err: torch.Tensor, softcap: float = 0.0,
                             slopes: Optional[torch.Tensor] = None,
                             sinks: Optional[torch.Tensor] = None, value_dim: Optional[int] = None,
-                            keep_first: int = 0, out_scale: float = 1.0) -> None:
+                            keep_first: int = 0, out_scale: float = 1.0,
+                            v_stride: int = 0) -> None:
     """Attention of every token row over its request's pages, any sizes.  ``softcap``,
     ``slopes`` (float32 ``[nh]``) and ``sinks`` (float32 ``[nh]``) change the scores as
     ``config.specs.ScoreSpec`` says; by default nothing is changed.  ``value_dim``: size of a
     value head where it differs from ``d``.  ``keep_first``: with a window, the request's
     first that many tokens stay visible behind it.  ``q`` and ``out`` may be column blocks of
     wider buffers (rows ``nh * d`` and ``nh * value_dim`` long); ``out_scale`` multiplies the
-    result."""
+    result.  ``v_stride``: elements between the value rows of neighbouring tokens of a page
+    (0: ``value_dim``); with ``v_cache = k_cache`` and ``v_stride = d`` a token's value is the
+    first ``value_dim`` numbers of its key."""
     T = q.shape[0]
     dv = d if value_dim is None else int(value_dim)
-    if d > 256 or dv > 256:
-        raise KernelError(f"attention: head sizes {d}, {dv} are not supported (at most 256)")
+    if d > GENERIC_MAX_HEAD_DIM or dv > GENERIC_MAX_VALUE_DIM:
+        raise KernelError(f"attention: head sizes {d}, {dv} are not supported (at most "
+                          f"{GENERIC_MAX_HEAD_DIM}, {GENERIC_MAX_VALUE_DIM})")
     if q.stride(1) != 1 or out.stride(1) != 1:
         raise KernelError("attention: rows of q and out must be contiguous")
     for name, t in (("slopes", slopes), ("sinks", sinks)):
@@ -247,9 +266,10 @@ def paged_attention_generic(q: torch.Tensor, k_cache: torch.Tensor, v_cache: tor
         _c_int(nkv), _c_int(d), _c_int(k_cache.shape[2]), _c_int(k_cache.shape[0]),
         _c_int(window or 0), _c_float(scale), _c_float(softcap), _ptr(slopes), _ptr(sinks),
         _c_int(_dtype_code(q)), _ptr(err), _c_int(dv), _c_int(keep_first), _c_ll(q.stride(0)),
-        _c_ll(out.stride(0)), _c_float(out_scale), _stream())
+        _c_ll(out.stride(0)), _c_float(out_scale), _c_ll(v_stride), _stream())
 
 
+GENERIC_MAX_HEAD_DIM, GENERIC_MAX_VALUE_DIM = 1024, 512
 DECODE_HEAD_DIMS = (32, 64, 96, 128, 256)
 DECODE_SPLIT_KEYS = 128
 
@@ -436,15 +456,24 @@ def conv_encode(proj: torch.Tensor, conv_w: Optional[torch.Tensor], taps: int,
                 slots: Optional[torch.Tensor], q_out: torch.Tensor,
                 k_cache: Optional[torch.Tensor], v_cache: Optional[torch.Tensor], nh: int,
                 nkv: int, dk: int, dv: int, unit_norm: bool, eps: float,
-                err: torch.Tensor) -> None:
+                err: torch.Tensor, pre_factor: Optional[torch.Tensor] = None,
+                pre_weight: Optional[torch.Tensor] = None, rot_magnitude: float = 1.0) -> None:
     """``proj`` rows hold ``[q: nh dk | k: nkv dk | v: nkv dv]`` (a column block of a wider
     buffer is fine).  Per channel a causal convolution over the request's tokens with
     ``conv_w`` float32 ``[channels, taps]`` (``taps`` 0: none), whose reach behind the
     step's first row is read from ``state`` float32 ``[slots, (taps-1) * channels]`` (a column
     block of the slots' storage); then q and k turned by the position (``inv_freq``), each
     head of them divided by its root mean square when ``unit_norm``; q to ``q_out``, k and v
-    into the pages at ``slots``.  The state is not changed: see :func:`conv_state_shift`."""
+    into the pages at ``slots``.  The state is not changed: see :func:`conv_state_shift`.
+    ``pre_factor`` float32 ``[T, 2]`` and ``pre_weight`` float32 ``[(nh + nkv) dk]``: q and k are
+    multiplied by their token's factor and their channel's weight before the rotation (a norm
+    over a whole projection: :func:`section_rms` takes the factors).  ``rot_magnitude``
+    multiplies cosines and sines."""
     T = proj.shape[0]
+    if pre_factor is not None:
+        _want(pre_factor, torch.float32, "pre_factor"); _want(pre_weight, torch.float32, "pre_weight")
+        if tuple(pre_factor.shape) != (T, 2) or pre_weight.numel() != (nh + nkv) * dk:
+            raise KernelError("conv_encode: pre_factor must be [T, 2], pre_weight [(nh + nkv) dk]")
     C = nh * dk + nkv * (dk + dv)
     if proj.stride(1) != 1 or proj.shape[1] != C or q_out.stride(1) != 1:
         raise KernelError("conv_encode: proj must be [T, nh dk + nkv (dk + dv)] with contiguous rows")
@@ -476,7 +505,7 @@ def conv_encode(proj: torch.Tensor, conv_w: Optional[torch.Tensor], taps: int,
          _ptr(slots), _ptr(q_out), _c_ll(q_out.stride(0)), _ptr(k_cache), _ptr(v_cache), _c_int(T),
          _c_int(nh), _c_int(nkv), _c_int(dk), _c_int(dv), _c_int(page_size), _c_ll(num_slots),
          _c_int(1 if unit_norm else 0), _c_float(eps), _c_int(_dtype_code(proj)), _ptr(table),
-         _ptr(err), _stream())
+         _ptr(err), _ptr(pre_factor), _ptr(pre_weight), _c_float(rot_magnitude), _stream())
 
 
 def conv_state_shift(proj: torch.Tensor, state: torch.Tensor, state_slots: torch.Tensor,
@@ -501,14 +530,14 @@ def retention_scan(proj: torch.Tensor, q_off: int, k_off: int, v_off: int, decay
                    inv_freq: Optional[torch.Tensor], positions: torch.Tensor,
                    state: torch.Tensor, q_start: torch.Tensor, state_slots: torch.Tensor,
                    o_raw: torch.Tensor, B: int, heads: int, dk: int, dv: int, k_scale: float,
-                   err: torch.Tensor, max_q: int = 0) -> None:
+                   err: torch.Tensor, max_q: int = 0, silu: bool = False) -> None:
     """The recurrence ``S <- decay_h S + k v^T, o = S^T q`` over every request's tokens of the
     step.  ``proj`` rows hold q (``heads dk`` numbers from column ``q_off``), k (from
     ``k_off``) and v (``heads dv`` from ``v_off``); q and k are turned by the position
     (``inv_freq`` float32, None: not) and k multiplied by ``k_scale``.  ``state`` float32
     ``[slots, heads * dv * dk]`` (a column block of the slots' storage); ``o_raw`` float32
     ``[T, heads dv]``.  ``max_q``: the most tokens one request brings to the step, if the
-    caller knows it (0: not known)."""
+    caller knows it (0: not known).  ``silu``: q, k and v pass silu first."""
     _want(decays, torch.float32, "decays"); _want(o_raw, torch.float32, "o_raw")
     if proj.stride(1) != 1 or dk > RETENTION_MAX_QK_DIM:
         raise KernelError(f"retention_scan: contiguous rows and a key size of at most "
@@ -528,7 +557,7 @@ def retention_scan(proj: torch.Tensor, q_off: int, k_off: int, v_off: int, decay
          _ptr(positions), _ptr(state), _c_ll(state.stride(0)), _ptr(q_start), _ptr(state_slots),
          _c_int(state.shape[0]), _ptr(o_raw), _ptr(qk), _c_int(T), _c_int(B),
          _c_int(max_q if max_q > 0 else T), _c_int(heads), _c_int(dk), _c_int(dv), _c_float(k_scale), _c_int(_dtype_code(proj)), _ptr(err),
-         _stream())
+         _c_int(1 if silu else 0), _stream())
     global _launches
     _launches += 1          # two kernels: the rotation and the scan
 
@@ -544,6 +573,172 @@ def retention_out(o_raw: torch.Tensor, proj: torch.Tensor, g_off: int, out: torc
     _run("retention_out", lib().bf_retention_out, _ptr(o_raw), _ptr(proj), _c_ll(proj.stride(0)),
          _c_ll(g_off), _ptr(out), _c_ll(out.stride(0)), _c_int(T), _c_int(heads), _c_int(dv),
          _c_float(eps), _c_float(out_scale), _c_int(_dtype_code(proj)), _stream())
+
+
+# ------------------------------------------- between a mixer's projection and its core
+def section_rms(x: torch.Tensor, off0: int, n0: int, off1: int, n1: int, eps: float,
+                out: torch.Tensor) -> None:
+    """``out[t, s] = rsqrt(mean(x[t, off_s : off_s + n_s]^2) + eps)`` for two column sections
+    of every row: the factors of RMS norms over whole projections."""
+    T = x.shape[0]
+    _want(out, torch.float32, "out")
+    if x.stride(1) != 1 or tuple(out.shape) != (T, 2):
+        raise KernelError("section_rms: contiguous rows and out [T, 2]")
+    _run("section_rms", lib().bf_section_rms, _ptr(x), _c_ll(x.stride(0)), _c_int(off0),
+         _c_int(n0), _c_int(off1), _c_int(n1), _c_float(eps), _ptr(out), _c_int(T),
+         _c_int(_dtype_code(x)), _stream())
+
+
+def latent_encode(proj: torch.Tensor, q_off: int, kv_off: int, norm_w: torch.Tensor, eps: float,
+                  inv_freq: Optional[torch.Tensor], interleaved: bool, rot_magnitude: float,
+                  positions: torch.Tensor, slots: Optional[torch.Tensor], q_abs: torch.Tensor,
+                  cache: Optional[torch.Tensor], heads: int, d: int, dr: int, rank: int,
+                  err: torch.Tensor) -> None:
+    """Attention over a cached latent, before the scores: ``proj`` rows hold ``heads`` query
+    heads of ``[d plain | dr rotated]`` from ``q_off`` and ``[rank | dr]`` from ``kv_off``.
+    The cache row of a token (pages ``[pages, 1, page_size, rank + dr]``, at ``slots``)
+    becomes ``[rmsnorm(first rank) * norm_w | rotated dr]``; ``q_abs [T, heads, rank + dr]``
+    gets every head's rotated part at ``[rank, rank + dr)`` and is otherwise left alone."""
+    T = proj.shape[0]
+    _want(norm_w, torch.float32, "norm_w")
+    if proj.stride(1) != 1 or not q_abs.is_contiguous() or q_abs.dtype != proj.dtype:
+        raise KernelError("latent_encode: contiguous rows, q_abs contiguous and of proj's type")
+    if tuple(q_abs.shape) != (T, heads, rank + dr) or norm_w.numel() != rank:
+        raise KernelError("latent_encode: q_abs must be [T, heads, rank + dr], norm_w [rank]")
+    rot_half = 0 if inv_freq is None else inv_freq.numel()
+    page_size, num_slots = 1, 0
+    if cache is not None:
+        if not cache.is_contiguous() or cache.shape[1] != 1 or cache.shape[3] != rank + dr:
+            raise KernelError("latent_encode: pages must be contiguous [pages, 1, size, rank + dr]")
+        page_size, num_slots = cache.shape[2], cache.shape[0] * cache.shape[2]
+    _run("latent_encode", lib().bf_latent_encode, _ptr(proj), _c_ll(proj.stride(0)), _c_ll(q_off),
+         _c_ll(kv_off), _ptr(norm_w), _c_float(eps), _ptr(inv_freq), _c_int(rot_half),
+         _c_int(1 if interleaved else 0), _c_float(rot_magnitude), _ptr(positions),
+         _ptr(slots if cache is not None else None), _ptr(q_abs), _ptr(cache), _c_int(T),
+         _c_int(heads), _c_int(d), _c_int(dr), _c_int(rank), _c_int(page_size), _c_ll(num_slots),
+         _c_int(_dtype_code(proj)), _ptr(err), _stream())
+
+
+def delta_encode(proj: torch.Tensor, conv_w: Optional[torch.Tensor], taps: int,
+                 state: Optional[torch.Tensor], state_slots: torch.Tensor,
+                 seq_of_token: torch.Tensor, q_start: torch.Tensor, b_off: int, a_off: int,
+                 A_log: torch.Tensor, dt_bias: torch.Tensor, qkv: torch.Tensor,
+                 gates: torch.Tensor, heads: int, qk_heads: int, dk: int, dv: int,
+                 unit_eps: float, q_scale: float, err: torch.Tensor) -> None:
+    """The gated delta rule's inputs.  ``proj`` rows hold ``[q: qk_heads dk | k: qk_heads dk |
+    v: heads dv]`` from column 0 and one logit per value head at ``b_off`` and at ``a_off``.
+    The first block passes a causal convolution per channel (``conv_w`` float32 ``[channels,
+    taps]``, reach behind the step's first row from ``state`` float32 ``[slots, (taps-1)
+    channels]``) and silu; q and k heads become unit vectors, q times ``q_scale``.  ``qkv``
+    float32 ``[T, channels]``; ``gates`` float32 ``[T, 2, heads]``: ``sigmoid(b)`` and
+    ``exp(-exp(A_log) softplus(a + dt_bias))``.  The state is not changed: see
+    :func:`conv_state_shift`."""
+    T = proj.shape[0]
+    C = 2 * qk_heads * dk + heads * dv
+    for t, n in ((A_log, "A_log"), (dt_bias, "dt_bias"), (qkv, "qkv"), (gates, "gates")):
+        _want(t, torch.float32, n)
+    if proj.stride(1) != 1 or tuple(qkv.shape) != (T, C) or tuple(gates.shape) != (T, 2, heads):
+        raise KernelError("delta_encode: contiguous rows, qkv [T, channels], gates [T, 2, heads]")
+    if taps > CONV_MAX_TAPS:
+        raise KernelError(f"delta_encode: at most {CONV_MAX_TAPS} taps")
+    if taps >= 1:
+        _want(conv_w, torch.float32, "conv_w")
+        if tuple(conv_w.shape) != (C, taps):
+            raise KernelError("delta_encode: conv_w must be [channels, taps]")
+    if taps > 1 and (state.dtype != torch.float32 or state.stride(1) != 1
+                     or state.shape[1] != (taps - 1) * C):
+        raise KernelError("delta_encode: state must be float32 [slots, (taps-1) * channels]")
+    has_state = taps > 1
+    _run("delta_encode", lib().bf_delta_encode, _ptr(proj), _c_ll(proj.stride(0)),
+         _ptr(conv_w if taps >= 1 else None), _c_int(taps), _ptr(state if has_state else None),
+         _c_ll(state.stride(0) if has_state else 0), _ptr(state_slots),
+         _c_int(state.shape[0] if has_state else 0), _ptr(seq_of_token), _ptr(q_start),
+         _c_ll(b_off), _c_ll(a_off), _ptr(A_log), _ptr(dt_bias), _ptr(qkv), _ptr(gates), _c_int(T),
+         _c_int(heads), _c_int(qk_heads), _c_int(dk), _c_int(dv), _c_float(unit_eps),
+         _c_float(q_scale), _c_int(_dtype_code(proj)), _ptr(err), _stream())
+
+
+DELTA_MAX_QK_DIM = 1024
+
+
+def delta_scan(qkv: torch.Tensor, gates: torch.Tensor, state: torch.Tensor,
+               q_start: torch.Tensor, state_slots: torch.Tensor, o_raw: torch.Tensor, B: int,
+               heads: int, qk_heads: int, dk: int, dv: int, err: torch.Tensor,
+               max_q: int = 0) -> None:
+    """The recurrence ``S <- g S; u = beta (v - S^T k); S <- S + k u^T; o = S^T q`` over every
+    request's tokens of the step, from :func:`delta_encode`'s ``qkv`` and ``gates``.  ``state``
+    float32 ``[slots, heads * dv * dk]`` (a column block of the slots' storage); ``o_raw``
+    float32 ``[T, heads dv]``."""
+    T = qkv.shape[0]
+    for t, n in ((qkv, "qkv"), (gates, "gates"), (o_raw, "o_raw")):
+        _want(t, torch.float32, n)
+    if (state.dtype != torch.float32 or state.stride(1) != 1
+            or state.shape[1] != heads * dk * dv or dk > DELTA_MAX_QK_DIM):
+        raise KernelError("delta_scan: state must be float32 [slots, heads * dk * dv]")
+    _run("delta_scan", lib().bf_delta_scan, _ptr(qkv), _ptr(gates), _ptr(state),
+         _c_ll(state.stride(0)), _ptr(q_start), _ptr(state_slots), _c_int(state.shape[0]),
+         _ptr(o_raw), _c_int(T), _c_int(B), _c_int(max_q if max_q > 0 else T), _c_int(heads),
+         _c_int(qk_heads), _c_int(dk), _c_int(dv), _ptr(err), _stream())
+
+
+def gated_norm_out(o_raw: torch.Tensor, proj: torch.Tensor, g_off: int,
+                   weight: Optional[torch.Tensor], out: torch.Tensor, heads: int, dv: int,
+                   eps: float, over_all: bool = False, gate: str = "silu",
+                   out_scale: float = 1.0) -> None:
+    """``out = o_raw / rms(o_raw) * weight * act(proj[:, g_off:]) * out_scale``: the root mean
+    square per head, or over all heads of a token (``over_all``); ``weight`` None, float32
+    ``[dv]`` (shared by the heads) or ``[heads dv]``; ``gate`` "silu" or "sigmoid".  ``out``
+    may be a column block of a wider buffer."""
+    _want(o_raw, torch.float32, "o_raw")
+    T = o_raw.shape[0]
+    if out.stride(1) != 1 or out.dtype != proj.dtype or proj.stride(1) != 1:
+        raise KernelError("gated_norm_out: rows must be contiguous, out of the projection's type")
+    w_mode = 0
+    if weight is not None:
+        _want(weight, torch.float32, "weight")
+        if weight.numel() == dv and heads > 1:
+            w_mode = 1
+        elif weight.numel() == heads * dv:
+            w_mode = 2
+        else:
+            raise KernelError("gated_norm_out: weight must have dv or heads * dv numbers")
+    if gate not in ("silu", "sigmoid"):
+        raise KernelError(f"gated_norm_out: unknown gate {gate!r}")
+    _run("gated_norm_out", lib().bf_gated_norm_out, _ptr(o_raw), _ptr(proj),
+         _c_ll(proj.stride(0)), _c_ll(g_off), _ptr(weight), _c_int(w_mode),
+         _c_int(1 if over_all else 0), _c_int(1 if gate == "sigmoid" else 0), _ptr(out),
+         _c_ll(out.stride(0)), _c_int(T), _c_int(heads), _c_int(dv), _c_float(eps),
+         _c_float(out_scale), _c_int(_dtype_code(proj)), _stream())
+
+
+def head_gate_mul(x: torch.Tensor, gate: torch.Tensor, heads: int, dv: int) -> None:
+    """``x[t, h, :] *= sigmoid(gate[t, h])``; ``x [T, heads dv]`` contiguous, ``gate`` a view
+    ``[T, heads]`` of rows of the same type."""
+    if not x.is_contiguous() or gate.stride(1) != 1 or gate.dtype != x.dtype:
+        raise KernelError("head_gate_mul: x contiguous, gate rows contiguous and of x's type")
+    _run("head_gate_mul", lib().bf_head_gate_mul, _ptr(x), _ptr(gate), _c_ll(gate.stride(0)),
+         _c_int(x.shape[0]), _c_int(heads), _c_int(dv), _c_int(_dtype_code(x)), _stream())
+
+
+def stream_inject(resid: torch.Tensor, delta: Optional[torch.Tensor],
+                  table: Optional[torch.Tensor], ids: Optional[torch.Tensor], scale: float,
+                  vec: Optional[torch.Tensor], err: torch.Tensor) -> None:
+    """``resid[t] += delta[t] + table[ids[t]] * scale + vec``; each of the three may be None."""
+    _want(resid, torch.float32, "resid")
+    T, width = resid.shape
+    if delta is not None and (not delta.is_contiguous() or delta.shape != resid.shape):
+        raise KernelError("stream_inject: delta must be contiguous and of the stream's shape")
+    if vec is not None:
+        _want(vec, torch.float32, "vec")
+        if vec.numel() != width:
+            raise KernelError("stream_inject: vec must have the stream's width")
+    if table is not None:
+        _want(ids, torch.int32, "ids")
+    _run("stream_inject", lib().bf_stream_inject, _ptr(resid), _ptr(delta),
+         _c_int(_dtype_code(delta) if delta is not None else 0), _ptr(table),
+         _c_int(_dtype_code(table) if table is not None else 0), _ptr(ids),
+         _c_int(table.shape[0] if table is not None else 0), _c_float(scale), _ptr(vec),
+         _c_int(T), _c_int(width), _ptr(err), _stream())
 
 
 # ---------------------------------------------------------------- mixture of experts
@@ -841,6 +1036,21 @@ def sgemm_nt(a: torch.Tensor, w: torch.Tensor, out: torch.Tensor) -> None:
     _run("sgemm_nt", lib().bf_sgemm_nt, _ptr(a), _ptr(w), _ptr(out), _c_int(M), _c_int(N), _c_int(K),
                              _c_ll(a.stride(0)), _c_ll(w.stride(0)), _c_ll(out.stride(0)),
                              _stream())
+
+
+def sgemm_nt_batched(a: torch.Tensor, w: torch.Tensor, out: torch.Tensor) -> None:
+    """out[:, b] = a[:, b] @ w[b]^T for every b, in true 32-bit arithmetic: ``a [M, B, K]`` and
+    ``out [M, B, N]`` may be strided views (innermost stride 1), ``w [B, N, K]``."""
+    for t, n in ((a, "a"), (w, "w"), (out, "out")):
+        if t.dtype != torch.float32 or t.stride(-1) != 1 or t.dim() != 3:
+            raise KernelError(f"sgemm_nt_batched: {n} must be a float32 [.., .., ..] with contiguous rows")
+    M, Bn, K = a.shape
+    N = w.shape[1]
+    if w.shape != (Bn, N, K) or out.shape != (M, Bn, N):
+        raise KernelError("sgemm_nt_batched: shapes do not agree")
+    _run("sgemm_nt_batched", lib().bf_sgemm_nt_batched, _ptr(a), _ptr(w), _ptr(out), _c_int(M),
+         _c_int(N), _c_int(K), _c_ll(a.stride(0)), _c_ll(w.stride(1)), _c_ll(out.stride(0)),
+         _c_int(Bn), _c_ll(a.stride(1)), _c_ll(w.stride(0)), _c_ll(out.stride(1)), _stream())
 
 
 _num_sms = {}

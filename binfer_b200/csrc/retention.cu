@@ -8,6 +8,8 @@
 // ([dv][dk]: the dk numbers that one output column needs lie side by side), and is carried
 // from step to step, so a prompt can be cut anywhere.
 //
+// With `act` 1, q, k and v pass silu first (lightning attention).
+//
 // retention_encode: q and k of every (token, head), turned and scaled, as float rows
 // `qk [T][2][H][dk]` (one warp per (token, head); the scan's blocks, several per head, read
 // them from there instead of each turning them again).
@@ -38,7 +40,7 @@ __global__ void retention_encode_kernel(const A* __restrict__ proj, long long st
                                         const float* __restrict__ inv_freq, int rot_half,
                                         const int* __restrict__ positions,
                                         float* __restrict__ qk, int T, int H, int dk,
-                                        float k_scale) {
+                                        float k_scale, int act) {
   const long long item = ((long long)blockIdx.x * blockDim.x + threadIdx.x) >> 5;
   const int lane = threadIdx.x & 31;
   if (item >= (long long)T * H) return;
@@ -49,12 +51,20 @@ __global__ void retention_encode_kernel(const A* __restrict__ proj, long long st
   const float pos = (float)positions[t];
   for (int i = lane; i < dk; i += 32) {
     float qv = bf_ld(row + q_off + i), kv = bf_ld(row + k_off + i);
+    if (act) {
+      qv = qv / (1.f + expf(-qv));
+      kv = kv / (1.f + expf(-kv));
+    }
     if (i < 2 * rot_half) {
       const int m = i < rot_half ? i : i - rot_half;
       const int o = i < rot_half ? i + rot_half : i - rot_half;
       float sn, cs;
       sincosf(pos * inv_freq[m], &sn, &cs);
-      const float qo2 = bf_ld(row + q_off + o), ko2 = bf_ld(row + k_off + o);
+      float qo2 = bf_ld(row + q_off + o), ko2 = bf_ld(row + k_off + o);
+      if (act) {
+        qo2 = qo2 / (1.f + expf(-qo2));
+        ko2 = ko2 / (1.f + expf(-ko2));
+      }
       qv = i < rot_half ? qv * cs - qo2 * sn : qv * cs + qo2 * sn;
       kv = i < rot_half ? kv * cs - ko2 * sn : kv * cs + ko2 * sn;
     }
@@ -76,7 +86,7 @@ __global__ void __launch_bounds__(RET_THREADS) retention_scan_kernel(
     const float* __restrict__ qk, const float* __restrict__ decays, float* __restrict__ state,
     long long state_stride, const int* __restrict__ q_start, const int* __restrict__ state_slots,
     int n_slots, float* __restrict__ o_raw, int H, int dk, int dv, int KS, int stage,
-    int* __restrict__ err) {
+    int* __restrict__ err, int act) {
   extern __shared__ __align__(16) float sh[];
   const int cols = RET_THREADS / KS * CV;
   const int dkp = KS * R;                   // dk rounded up to what the lanes of a column hold
@@ -147,9 +157,11 @@ __global__ void __launch_bounds__(RET_THREADS) retention_scan_kernel(
     }
     for (int idx = tid; idx < sn * cols; idx += RET_THREADS) {
       const int c = idx / cols, j = idx % cols;
-      vd[idx] = col0 + j < dv
+      float x = col0 + j < dv
                     ? bf_ld(proj + (size_t)(t0 + s0 + c) * stride + v_off + (size_t)h * dv + col0 + j)
                     : 0.f;
+      if (act) x = x / (1.f + expf(-x));
+      vd[idx] = x;
     }
     asm volatile("cp.async.commit_group;" ::);
   };
@@ -262,7 +274,7 @@ BF_EXPORT int bf_retention_scan(
     const float* decays, const float* inv_freq, int rot_half, const int* positions, float* state,
     long long state_stride, const int* q_start, const int* state_slots, int n_slots, float* o_raw,
     float* qk, int T, int B, int max_q, int H, int dk, int dv, float k_scale, int act_dtype,
-    int* err, cudaStream_t stream) {
+    int* err, int act, cudaStream_t stream) {
   // qk: scratch, float [T][2][H][dk]; max_q: the most tokens one request brings (a hint that
   // sizes the staging buffers: single tokens leave room for more blocks an SM)
   if (B <= 0 || T <= 0) return 0;
@@ -273,11 +285,11 @@ BF_EXPORT int bf_retention_scan(
     if (act_dtype == BF_DTYPE_F32)
       retention_encode_kernel<float><<<(unsigned)blocks, threads, 0, stream>>>(
           (const float*)proj, stride, q_off, k_off, inv_freq, rot_half, positions, qk, T, H, dk,
-          k_scale);
+          k_scale, act);
     else
       retention_encode_kernel<__nv_bfloat16><<<(unsigned)blocks, threads, 0, stream>>>(
           (const __nv_bfloat16*)proj, stride, q_off, k_off, inv_freq, rot_half, positions, qk, T,
-          H, dk, k_scale);
+          H, dk, k_scale, act);
     const int e = bf_launch_status();
     if (e) return e;
   }
@@ -304,7 +316,7 @@ BF_EXPORT int bf_retention_scan(
                            cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);            \
     retention_scan_kernel<AT, RR, CC><<<grid, RET_THREADS, smem, stream>>>(                    \
         (const AT*)proj, stride, v_off, qk, decays, state, state_stride, q_start, state_slots, \
-        n_slots, o_raw, H, dk, dv, KS, stage, err);                                            \
+        n_slots, o_raw, H, dk, dv, KS, stage, err, act);                                       \
   }
 #define RET_PICK(AT)                                             \
   if (R == 32) RET_GO(AT, 32, 1)                                  \

@@ -19,8 +19,12 @@
 template <int BM, int BN, int BK, int TM, int TN>
 __global__ void __launch_bounds__((BM / TM) * (BN / TN))
 sgemm_nt_kernel(const float* __restrict__ A, const float* __restrict__ W, float* __restrict__ C,
-                int M, int N, int K, long long lda, long long ldw, long long ldc) {
+                int M, int N, int K, long long lda, long long ldw, long long ldc,
+                long long batch_a, long long batch_w, long long batch_c) {
   constexpr int THREADS = (BM / TM) * (BN / TN);
+  A += blockIdx.z * batch_a;             // one product per blockIdx.z (strides 0: one product)
+  W += blockIdx.z * batch_w;
+  C += blockIdx.z * batch_c;
   __shared__ float As[BK][BM + 4];
   __shared__ float Ws[BK][BN + 4];
   const int tid = threadIdx.x;
@@ -81,19 +85,39 @@ sgemm_nt_kernel(const float* __restrict__ A, const float* __restrict__ W, float*
   }
 }
 
-BF_EXPORT int bf_sgemm_nt(const float* A, const float* W, float* C, int M, int N, int K,
-                          long long lda, long long ldw, long long ldc, cudaStream_t stream) {
-  if (M <= 0 || N <= 0) return 0;
+static int sgemm_nt_launch(const float* A, const float* W, float* C, int M, int N, int K,
+                           long long lda, long long ldw, long long ldc, int batch,
+                           long long batch_a, long long batch_w, long long batch_c,
+                           cudaStream_t stream) {
+  if (M <= 0 || N <= 0 || batch <= 0) return 0;
   if (M <= 16) {
-    dim3 grid((N + 63) / 64, (M + 15) / 16);
-    sgemm_nt_kernel<16, 64, 16, 1, 4><<<grid, 256, 0, stream>>>(A, W, C, M, N, K, lda, ldw, ldc);
+    dim3 grid((N + 63) / 64, (M + 15) / 16, batch);
+    sgemm_nt_kernel<16, 64, 16, 1, 4><<<grid, 256, 0, stream>>>(A, W, C, M, N, K, lda, ldw, ldc,
+                                                               batch_a, batch_w, batch_c);
   } else if (M <= 64) {
-    dim3 grid((N + 127) / 128, (M + 31) / 32);
-    sgemm_nt_kernel<32, 128, 16, 2, 8><<<grid, 256, 0, stream>>>(A, W, C, M, N, K, lda, ldw, ldc);
+    dim3 grid((N + 127) / 128, (M + 31) / 32, batch);
+    sgemm_nt_kernel<32, 128, 16, 2, 8><<<grid, 256, 0, stream>>>(A, W, C, M, N, K, lda, ldw, ldc,
+                                                                batch_a, batch_w, batch_c);
   } else {
-    dim3 grid((N + 127) / 128, (M + 127) / 128);
+    dim3 grid((N + 127) / 128, (M + 127) / 128, batch);
     sgemm_nt_kernel<128, 128, 16, 8, 8><<<grid, 256, 0, stream>>>(A, W, C, M, N, K, lda, ldw,
-                                                                 ldc);
+                                                                 ldc, batch_a, batch_w, batch_c);
   }
   return bf_launch_status();
+}
+
+BF_EXPORT int bf_sgemm_nt(const float* A, const float* W, float* C, int M, int N, int K,
+                          long long lda, long long ldw, long long ldc, cudaStream_t stream) {
+  return sgemm_nt_launch(A, W, C, M, N, K, lda, ldw, ldc, 1, 0, 0, 0, stream);
+}
+
+// `batch` products at once: product b reads A + b batch_a and W + b batch_w and writes
+// C + b batch_c (heads that lie side by side in a token's row, each with a matrix of its own).
+BF_EXPORT int bf_sgemm_nt_batched(const float* A, const float* W, float* C, int M, int N, int K,
+                                  long long lda, long long ldw, long long ldc, int batch,
+                                  long long batch_a, long long batch_w, long long batch_c,
+                                  cudaStream_t stream) {
+  if (batch > 65535) return (int)cudaErrorInvalidValue;
+  return sgemm_nt_launch(A, W, C, M, N, K, lda, ldw, ldc, batch, batch_a, batch_w, batch_c,
+                         stream);
 }

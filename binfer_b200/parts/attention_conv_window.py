@@ -3,8 +3,10 @@ the request's first tokens, as a mixer part.
 
 Order of operations: one product for q, k and v; a causal convolution over time on every
 channel of the three (the projected values of a request's last ``taps - 1`` tokens are
-per-request state, so a prompt can be cut anywhere); rotation of q and k; each q and k head
-divided by its root mean square, after the rotation; k and v into the pages; attention in
+per-request state, so a prompt can be cut anywhere); optionally an RMS norm with weights over
+the whole q projection and the whole k projection, all heads at once; rotation of q and k;
+optionally each q and k head divided by its root mean square, after the rotation; k and v
+into the pages; scores with an optional soft cap; attention in
 which position i sees j <= i with ``i - j < window`` or ``j < keep_first`` (kept tokens stay
 at their true positions) and whose softmax has a learned logit per head in its denominator;
 the output projection.  Every key, also those of the step's own tokens, is read from the
@@ -52,11 +54,16 @@ class ConvWindowAttention(Mixer):
         self.taps = max(0, int(spec.conv_taps))     # one tap: a factor per channel, no state
         self.position = (build_position(spec.position, self.dk, env)
                          if spec.position is not None else None)
-        if self.position is not None and self.position.inv_freq is None:
-            raise ValueError("this attention takes rotary encodings only")
+        if self.position is not None and (self.position.inv_freq is None
+                                          or getattr(self.position, "interleaved", False)
+                                          or getattr(self.position, "offset", 0)):
+            raise ValueError("this attention takes rotary encodings over the first sizes of a "
+                             "head, in halves, only")
+        if spec.proj_norm and self.taps:
+            raise ValueError("a norm over the whole projection goes without a convolution")
         self.names = dict(spec.names)
         self.in_rows, self.out_cols = self.channels, self.H * self.dv
-        self.w_in = self.w_out = self.conv_w = self.sinks = None
+        self.w_in = self.w_out = self.conv_w = self.sinks = self.proj_norm_w = None
 
     # ----------------------------------------------------------------- weights
     def _spec(self, role: str) -> ParamSpec:
@@ -66,6 +73,10 @@ class ConvWindowAttention(Mixer):
             return ParamSpec(self.prefix + self.names[role], base[role])
         if role == "sink":
             return ParamSpec(self.prefix + self.names["sink"], (self.H,), init="around_zero",
+                             role="vector")
+        if role in ("q_norm", "k_norm"):
+            return ParamSpec(self.prefix + self.names[role],
+                             (self.q_size if role == "q_norm" else self.k_size,), init="norm",
                              role="vector")
         src = role[:-5]                          # "q.conv" -> q
         return ParamSpec(self.prefix + self.names[src] + self.spec.conv_suffix,
@@ -77,6 +88,8 @@ class ConvWindowAttention(Mixer):
             roles += ["q.conv", "k.conv", "v.conv"]
         if self.spec.sinks:
             roles.append("sink")
+        if self.spec.proj_norm:
+            roles += ["q_norm", "k_norm"]
         return roles
 
     def param_specs(self) -> List[ParamSpec]:
@@ -90,6 +103,8 @@ class ConvWindowAttention(Mixer):
             self.conv_w = torch.cat([g("q.conv"), g("k.conv"), g("v.conv")], dim=0).contiguous()
         if self.spec.sinks:
             self.sinks = g("sink")
+        if self.spec.proj_norm:
+            self.proj_norm_w = torch.cat([g("q_norm"), g("k_norm")]).contiguous()
 
     # ------------------------------------------------------------ cache, state
     def kv_need(self) -> Optional[KVNeed]:
@@ -118,14 +133,19 @@ class ConvWindowAttention(Mixer):
         q = torch.empty((T, self.q_size), dtype=proj.dtype, device=proj.device)
         inv = self.position.inv_freq if self.position is not None else None
         state = view.state if self.taps > 1 else None
+        factors = None
+        if s.proj_norm:
+            factors = torch.empty((T, 2), dtype=torch.float32, device=proj.device)
+            ops.section_rms(proj, 0, self.q_size, self.q_size, self.k_size, s.norm_eps, factors)
         ops.conv_encode(proj, self.conv_w, self.taps, state, ctx.state_slots, ctx.seq_of_token,
                         ctx.q_start, inv, ctx.positions, ctx.slots[g], q, view.k_cache,
                         view.v_cache, self.H, self.G, self.dk, self.dv, s.unit_norm, s.norm_eps,
-                        ctx.err)
+                        ctx.err, pre_factor=factors, pre_weight=self.proj_norm_w,
+                        rot_magnitude=getattr(self.position, "magnitude", 1.0))
         if self.taps > 1:
             ops.conv_state_shift(proj, state, ctx.state_slots, ctx.q_start, ctx.B, self.taps)
         keep = s.keep_first if s.window is not None else 0
-        if (TENSOR_CORES and s.softmax_scale > 0
+        if (TENSOR_CORES and s.softmax_scale > 0 and not s.softcap
                 and ops.pwm_attention_takes(proj.dtype, self.H, self.G, self.dk, self.dv)):
             # bfloat16: tiles of (token, head of a group) rows on the tensor cores, prompt
             # portions and single tokens alike (the windowed kernel, without pooled blocks)
@@ -139,7 +159,7 @@ class ConvWindowAttention(Mixer):
         ops.paged_attention_generic(
             q, view.k_cache, view.v_cache, ctx.seq_of_token, ctx.positions, ctx.block_tables[g],
             out, self.H, self.G, self.dk, s.window, s.softmax_scale, ctx.err, sinks=self.sinks,
-            value_dim=self.dv, keep_first=keep, out_scale=out_scale)
+            value_dim=self.dv, keep_first=keep, out_scale=out_scale, softcap=s.softcap)
 
 
 register_mixer("conv_window_attention", ConvWindowAttention)

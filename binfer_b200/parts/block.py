@@ -2,7 +2,8 @@
 
 ``x += mixer(norm1(x)); x += ffn(norm2(x))`` (src/engine/batched_engine.ts:800-1314).
 Each sublayer's output is left pending on the residual stream and folded in by
-the next norm, this layer's or the following one's.
+the next norm, this layer's or the following one's.  A layer without a feed-forward
+(``LayerSpec.ffn`` None) has no second norm either.
 """
 from __future__ import annotations
 
@@ -20,14 +21,18 @@ class PreNormBlock(Part):
                  env: BuildEnv):
         p = names.layer_prefix.format(i=index)
         self.index = index
-        self.input_norm = build_norm(spec.norm, hidden_size, f"{p}{names.norm('input')}.weight", env)
+        sfx = names.norm_suffix
+        self.input_norm = build_norm(spec.norm, hidden_size, f"{p}{names.norm('input')}{sfx}", env)
         self.mixer = build_mixer(spec.mixer, hidden_size, f"{p}{names.mixer}.", env)
-        self.post_norm = build_norm(spec.norm, hidden_size,
-                                    f"{p}{names.norm('post_mixer')}.weight", env)
-        self.ffn = build_ffn(spec.ffn, hidden_size, f"{p}{names.ffn}.", env)
+        self.post_norm = self.ffn = None
+        if spec.ffn is not None:
+            self.post_norm = build_norm(spec.norm, hidden_size,
+                                        f"{p}{names.norm('post_mixer')}{sfx}", env)
+            self.ffn = build_ffn(spec.ffn, hidden_size, f"{p}{names.ffn}.", env)
 
     def parts(self) -> List[Part]:
-        return [self.input_norm, self.mixer, self.post_norm, self.ffn]
+        return [part for part in (self.input_norm, self.mixer, self.post_norm, self.ffn)
+                if part is not None]
 
     def param_specs(self):
         return [s for part in self.parts() for s in part.param_specs()]
@@ -42,6 +47,14 @@ class PreNormBlock(Part):
         can then be prepared by this block's last product."""
         h = self._for(self.mixer, self.input_norm.forward(stream))
         deferred = getattr(self.mixer, "forward_deferred", None)
+        if self.ffn is None:
+            nxt = successor if isinstance(successor, PreNormBlock) else None
+            if deferred is not None:
+                stream.add_linear(deferred(h, ctx, view), nxt.input_norm if nxt else None,
+                                  nxt.mixer if nxt else None)
+            else:
+                stream.add(self.mixer.forward(h, ctx, view))
+            return
         if deferred is not None:
             stream.add_linear(deferred(h, ctx, view), self.post_norm, self.ffn)
         else:

@@ -190,3 +190,23 @@ def linear_add_norm(x: torch.Tensor, w: torch.Tensor, resid: torch.Tensor,
     return ops.gemm_bf16_cluster_add_norm(x, w, resid, norm_w, eps, ops.error_word(x.device),
                                           *plan)
 
+
+
+def linear_heads(x: torch.Tensor, w: torch.Tensor, out: torch.Tensor) -> torch.Tensor:
+    """``out[:, h] = x[:, h] @ w[h]^T`` for every head h: ``x [T, H, K]`` and ``out [T, H, N]``
+    may be strided views of wider rows (innermost stride 1), ``w [H, N, K]`` contiguous.
+    float32: the engine's own FP32-FMA kernel, one launch for all heads; bfloat16: the
+    library's strided batched product with float accumulation."""
+    if x.dtype == torch.float32:
+        ops.sgemm_nt_batched(x, w, out)
+        return out
+    if x.dtype != torch.bfloat16 or w.dtype != torch.bfloat16:
+        raise TypeError(f"linear_heads: unsupported dtypes {x.dtype} x {w.dtype}")
+    prof = ops._profiler
+    if prof is not None:
+        prof.begin("cublas_bmm_bf16")
+    ops.count_library_launch()
+    torch.bmm(x.transpose(0, 1), w.transpose(1, 2), out=out.transpose(0, 1))
+    if prof is not None:
+        prof.end("cublas_bmm_bf16")
+    return out

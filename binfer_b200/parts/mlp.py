@@ -1,4 +1,6 @@
-"""Dense gated feed-forward (SwiGLU): ``down( silu(gate(x)) * up(x) )``.
+"""Dense gated feed-forward: ``down( act(gate(x)) * up(x) )``, ``act`` silu (SwiGLU) or the
+tanh form of gelu (``GatedMLPSpec.activation``; the products with the activation in their
+epilogue are silu's, another activation runs the product and the activation kernel).
 
 ``silu(g) = g / (1 + exp(-g))`` (cuda/kernels/bf16_kernels.cu:461-477).  The
 reference runs gate and up as two products (src/engine/batched_engine.ts:1243-1244);
@@ -27,8 +29,10 @@ FUSE_SWIGLU_FILL = 0.5
 
 class GatedMLP(FeedForward):
     def __init__(self, spec: GatedMLPSpec, hidden_size: int, prefix: str, env: BuildEnv):
-        if spec.activation != "silu":
-            raise ValueError(f"activation {spec.activation!r} is not supported (supported: 'silu')")
+        if spec.activation not in ops.GATE_ACTIVATIONS:
+            raise ValueError(f"activation {spec.activation!r} is not supported (supported: "
+                             f"{sorted(ops.GATE_ACTIVATIONS)})")
+        self.silu = spec.activation == "silu"
         if spec.bias:
             raise ValueError("feed-forward biases are not supported")
         self.spec, self.hidden, self.prefix, self.env = spec, hidden_size, prefix, env
@@ -55,20 +59,23 @@ class GatedMLP(FeedForward):
 
     def forward_deferred(self, x, ctx: StepContext) -> DeferredLinear:
         """Everything but the down projection (see ``GQAAttention.forward_deferred``)."""
-        if isinstance(x, ScaledRows) and (self.inter % 8 or self.inter < 256):
+        if isinstance(x, ScaledRows) and (self.inter % 8 or self.inter < 256 or not self.silu):
             x = x.dense()                  # the activation kernel takes the factor at other sizes only
         x, row_scale = split_scaled(x)
         h = torch.empty((x.shape[0], self.inter), dtype=x.dtype, device=x.device)
         if not self._project_fused(x, h, row_scale):
             gu = linear(x, self.w_gate_up)
-            ops.silu_mul(gu, h, row_scale=row_scale)
+            if self.silu:
+                ops.silu_mul(gu, h, row_scale=row_scale)
+            else:
+                ops.gated_act_mul(gu, h, self.spec.activation)
         return DeferredLinear(h, self.w_down)
 
     def _project_fused(self, x, h, row_scale) -> bool:
         """Few token rows in bfloat16: the stacked projection with the activation in its
         epilogue, one CTA a tile of gate rows and the up rows of the same outputs.  False,
         having done nothing, where that kernel does not run."""
-        if not FUSE_SWIGLU or x.dtype != torch.bfloat16 or self.inter % 8:
+        if not FUSE_SWIGLU or not self.silu or x.dtype != torch.bfloat16 or self.inter % 8:
             return False
         pair_from = pair_token_limit()
         if pair_from and x.shape[0] >= pair_from and row_scale is None:

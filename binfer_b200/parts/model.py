@@ -25,7 +25,9 @@ from .linear import linear
 
 # importing the modules registers the built-in parts
 from . import attention as _attention  # noqa: F401
+from . import attention_latent as _attention_latent  # noqa: F401
 from . import attention_pooled as _attention_pooled  # noqa: F401
+from . import delta_rule as _delta_rule  # noqa: F401
 from . import block as _block          # noqa: F401
 from . import block_sublayer_norm as _block_sublayer_norm  # noqa: F401
 from . import block_parallel as _block_parallel  # noqa: F401
@@ -51,7 +53,16 @@ class DecoderModel:
                           else ParamSpec(names.lm_head, (spec.vocab_size, spec.hidden_size)))
         self.embed: Optional[torch.Tensor] = None
         self.lm_head: Optional[torch.Tensor] = None
+        self.pass_spec = (None if spec.pass_table is None else
+                          ParamSpec(spec.pass_table[0], (int(spec.pass_table[1]), spec.hidden_size),
+                                    init="around_zero", role="vector"))
+        self.pass_table: Optional[torch.Tensor] = None
         for e, entry in enumerate(spec.schedule):
+            if entry.before is not None and entry.before.row is not None and not (
+                    self.pass_spec is not None
+                    and 0 <= entry.before.row < self.pass_spec.shape[0]):
+                raise ValueError(f"schedule entry {e} adds row {entry.before.row} of a table "
+                                 f"of pass vectors that the model lacks or that is shorter")
             if not 0 <= entry.layer < len(self.blocks):
                 raise ValueError(f"schedule entry {e} names layer {entry.layer}, "
                                  f"but there are {len(self.blocks)} layers")
@@ -67,6 +78,8 @@ class DecoderModel:
         for b in self.blocks:
             specs += b.param_specs()
         specs += self.final_norm.param_specs()
+        if self.pass_spec is not None:
+            specs.append(self.pass_spec)
         if self.head_spec is not None:
             specs.append(self.head_spec)
         return specs
@@ -85,6 +98,8 @@ class DecoderModel:
         for b in self.blocks:
             b.load(get)
         self.final_norm.load(get)
+        if self.pass_spec is not None:
+            self.pass_table = get(self.pass_spec)
         self.lm_head = self.embed if self.head_spec is None else get(self.head_spec)
 
     def weight_bytes(self) -> int:
@@ -140,12 +155,20 @@ class DecoderModel:
         for e, entry in enumerate(spec.schedule):
             ctx.entry = e
             block = self.blocks[entry.layer]
+            if entry.before is not None:
+                self._open_pass(stream, ctx, entry.before)
             if getattr(block, "takes_successor", False):
                 # a block may let its last product prepare the next block's first norm
-                nxt = self.blocks[spec.schedule[e + 1].layer] if e < last else None
+                # (not where the stream changes in between: the start of a pass)
+                nxt = (self.blocks[spec.schedule[e + 1].layer]
+                       if e < last and spec.schedule[e + 1].before is None else None)
                 block.forward(stream, ctx, views[e], nxt)
             else:
                 block.forward(stream, ctx, views[e])
+            if "layer_outputs" in ctx.scratch:
+                # for tests and debugging: the stream after every layer run, everything folded in
+                stream.flush()
+                ctx.scratch["layer_outputs"].append(stream.x.clone())
         R = ctx.logit_rows.shape[0]
         if R == 0:
             stream.flush()
@@ -155,6 +178,21 @@ class DecoderModel:
         if spec.logit_scale != 1.0:
             logits.mul_(spec.logit_scale)
         return logits
+
+
+    def _open_pass(self, stream: ResidualStream, ctx: StepContext, before) -> None:
+        """Fold the pending sublayer output into the stream together with what a pass starts
+        with: the embedding output again (gathered from the table anew, in float) and a row
+        of the pass table."""
+        if not before.embedding and before.row is None:
+            return
+        if stream.pending2 is not None:
+            stream.flush()
+        delta, stream.pending = stream.pending, None
+        stream.ready = stream.ready_for = stream.reading = None
+        ops.stream_inject(stream.x, delta, self.embed if before.embedding else None,
+                          ctx.token_ids, self.spec.embedding_scale,
+                          self.pass_table[before.row] if before.row is not None else None, ctx.err)
 
 
 def param_specs_for(spec: ModelSpec) -> List[ParamSpec]:

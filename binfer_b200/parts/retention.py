@@ -7,7 +7,9 @@ Per head, with a state ``S [dk, dv]`` that starts at zero for a new request::
     S <- decay_h S + k v^T          o = S^T q
 
 and the mixer returns ``W_o (o / rms_head(o) * silu(W_g h))``.  There is no softmax and no
-denominator.  The q, k, v and gate projections are one product against the stacked weight;
+denominator.  The spec's options give lightning attention: ``silu`` on the q, k and v
+projections, no factor on k, one root mean square over all heads of a token with a weight,
+and a sigmoid gate.  The q, k, v and gate projections are one product against the stacked weight;
 rotation, recurrence and the head norm are float whatever the engine's precision; the state
 lives in the cache manager's slots and is carried from step to step, so a prompt can be cut
 anywhere and a request can share a step with others.  ``w_in`` / ``w_out`` /
@@ -39,8 +41,19 @@ class RetentionMixer(Mixer):
         self.qk_size, self.v_size = self.heads * self.dk, self.heads * self.dv
         self.position = (build_position(spec.position, self.dk, env)
                          if spec.position is not None else None)
-        if self.position is not None and self.position.inv_freq is None:
-            raise ValueError("retention takes rotary encodings only")
+        if self.position is not None and (self.position.inv_freq is None
+                                          or getattr(self.position, "interleaved", False)
+                                          or getattr(self.position, "offset", 0)
+                                          or getattr(self.position, "magnitude", 1.0) != 1.0):
+            raise ValueError("retention takes plain rotary encodings in halves only")
+        if spec.activation not in (None, "silu"):
+            raise ValueError(f"retention: activation {spec.activation!r} is not supported")
+        if spec.norm_over not in ("head", "all") or spec.gate not in ("silu", "sigmoid"):
+            raise ValueError("retention: norm_over is 'head' or 'all', gate 'silu' or 'sigmoid'")
+        self.k_scale = self.dk ** -0.5 if spec.k_scale is None else float(spec.k_scale)
+        self.plain_out = (spec.norm_over == "head" and not spec.norm_weight
+                          and spec.gate == "silu")
+        self.norm_w = None
         self.decays = torch.tensor(spec.decays, dtype=torch.float64).to(torch.float32).to(env.device)
         self.names = dict(spec.names)
         self.in_rows, self.out_cols = 2 * self.qk_size + 2 * self.v_size, self.v_size
@@ -50,16 +63,21 @@ class RetentionMixer(Mixer):
     def _spec(self, role: str) -> ParamSpec:
         shape = {"q": (self.qk_size, self.hidden), "k": (self.qk_size, self.hidden),
                  "v": (self.v_size, self.hidden), "g": (self.v_size, self.hidden),
-                 "o": (self.hidden, self.v_size)}[role]
+                 "o": (self.hidden, self.v_size), "norm": (self.v_size,)}[role]
+        if role == "norm":
+            return ParamSpec(self.prefix + self.names[role], shape, init="norm", role="vector")
         return ParamSpec(self.prefix + self.names[role], shape)
 
     def param_specs(self) -> List[ParamSpec]:
-        return [self._spec(r) for r in ("q", "k", "v", "g", "o")]
+        roles = ("q", "k", "v", "g", "o") + (("norm",) if self.spec.norm_weight else ())
+        return [self._spec(r) for r in roles]
 
     def load(self, get: Callable[[ParamSpec], torch.Tensor]) -> None:
         g = lambda role: get(self._spec(role))          # noqa: E731
         self.w_in = torch.cat([g("q"), g("k"), g("v"), g("g")], dim=0).contiguous()
         self.w_out = g("o")
+        if self.spec.norm_weight:
+            self.norm_w = g("norm")
 
     # ------------------------------------------------------------------- state
     def state_need(self) -> Optional[StateNeed]:
@@ -78,10 +96,17 @@ class RetentionMixer(Mixer):
         inv = self.position.inv_freq if self.position is not None else None
         ops.retention_scan(proj, 0, self.qk_size, 2 * self.qk_size, self.decays, inv,
                            ctx.positions, view.state, ctx.q_start, ctx.state_slots, o_raw, ctx.B,
-                           self.heads, self.dk, self.dv, self.dk ** -0.5, ctx.err,
-                           max_q=1 if ctx.decode_only else ctx.max_q_len)
-        ops.retention_out(o_raw, proj, 2 * self.qk_size + self.v_size, out, self.heads, self.dv,
-                          self.spec.norm_eps, out_scale)
+                           self.heads, self.dk, self.dv, self.k_scale, ctx.err,
+                           max_q=1 if ctx.decode_only else ctx.max_q_len,
+                           silu=self.spec.activation == "silu")
+        g_off = 2 * self.qk_size + self.v_size
+        if self.plain_out:
+            ops.retention_out(o_raw, proj, g_off, out, self.heads, self.dv, self.spec.norm_eps,
+                              out_scale)
+        else:
+            ops.gated_norm_out(o_raw, proj, g_off, self.norm_w, out, self.heads, self.dv,
+                               self.spec.norm_eps, over_all=self.spec.norm_over == "all",
+                               gate=self.spec.gate, out_scale=out_scale)
 
 
 register_mixer("retention", RetentionMixer)
