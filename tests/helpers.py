@@ -476,3 +476,105 @@ def make_fikotar_dir(tmp_path, which, dtype=torch.float32, raw=None, tweak=None,
         tweak(w)
     save_file(w, os.path.join(d, "model.safetensors"))
     return d
+
+
+# ----------------------------------------------------------------- the looped design
+def _ket_latent(heads, dim, rot_dim, vdim, rank, base=10000.0, scale=None):
+    return {"heads": heads, "dim": dim, "rot_dim": rot_dim, "vdim": vdim, "kv_rank": rank,
+            "rot": {"base": base, "dims": rot_dim},
+            "scale": (dim + rot_dim) ** -0.5 if scale is None else scale}
+
+
+def _ket_delta(heads, kv_heads, dim, vdim, conv):
+    return {"heads": heads, "kv_heads": kv_heads, "dim": dim, "vdim": vdim, "conv": conv}
+
+
+def _ket_left(heads, kv_heads, dim, vdim, rot_dims, base=10000.0, scale=None, softcap=None,
+              scaling=None):
+    m = {"heads": heads, "kv_heads": kv_heads, "dim": dim, "vdim": vdim,
+         "rot": {"base": base, "dims": rot_dims},
+         "scale": dim ** -0.5 if scale is None else scale}
+    if softcap is not None:
+        m["softcap"] = softcap
+    if scaling is not None:
+        m["rot"]["scaling"] = dict(zip(("factor", "original", "fast", "slow"), scaling))
+    return m
+
+
+def _ket_right(heads, dim, vdim, decay):
+    return {"heads": heads, "dim": dim, "vdim": vdim, "decay": list(decay)}
+
+
+def _ket_layer(kind, mixer, ff=None):
+    return {"type": kind, "mixer": mixer, "mlp": None if ff is None else {"kind": "dense", "ff": ff}}
+
+
+def _ket_parallel(left, right, ls=1.0, rs=1.0, ff=None):
+    return _ket_layer("parallel", {"left": left, "right": right, "left_scale": ls,
+                                   "right_scale": rs}, ff)
+
+
+# the delta rule first; the first two layers walked twice; grouped heads; stretched waves and a
+# soft cap; the last layer without a feed-forward
+KET_A = {"architecture": "Ketopel", "vocab": 300, "width": 64, "norm": {"eps": 1e-5},
+         "embedding": {"scale": 2.0}, "loop": {"start": 0, "stop": 2, "times": 2},
+         "layers": [_ket_layer("delta", _ket_delta(4, 2, 16, 24, 3), ff=96),
+                    _ket_parallel(_ket_left(4, 2, 32, 16, 16, scale=0.2, softcap=20.0,
+                                            scaling=(8.0, 64, 4.0, 1.0)),
+                                  _ket_right(2, 16, 32, (0.9, 0.99)), ls=0.7, rs=1.2, ff=80),
+                    _ket_layer("latent_attention", _ket_latent(3, 24, 8, 20, 40, scale=0.2))]}
+# the loop runs to the last layer, three times; no grouping anywhere; values larger than keys
+# and no multiple of 32; the whole head rotated, no stretching, no soft cap; a decay of one;
+# convolutions of four taps and of one; a layer without a feed-forward inside the loop
+KET_B = {"architecture": "Ketopel", "vocab": 211, "width": 48, "norm": {"eps": 1e-6},
+         "embedding": {"scale": 1.0}, "loop": {"start": 1, "stop": 4, "times": 3},
+         "layers": [_ket_layer("latent_attention", _ket_latent(2, 16, 16, 16, 24, base=500.0), ff=64),
+                    _ket_parallel(_ket_left(3, 3, 24, 40, 24, base=500.0, scale=0.3),
+                                  _ket_right(3, 8, 8, (1.0, 0.5, 0.98)), ls=0.5, rs=0.5),
+                    _ket_layer("delta", _ket_delta(3, 3, 8, 8, 4), ff=56),
+                    _ket_layer("delta", _ket_delta(2, 1, 40, 12, 1), ff=40)]}
+# sizes that are multiples of two only: a width of 50, heads of 10 and 6, a vocabulary of 131;
+# one head; a "loop" of one pass over the last layer; no embedding scale given
+KET_C = {"architecture": "Ketopel", "vocab": 131, "width": 50, "norm": {"eps": 1e-5},
+         "loop": {"start": 2, "stop": 3, "times": 1},
+         "layers": [_ket_layer("delta", _ket_delta(2, 1, 6, 10, 2), ff=34),
+                    _ket_layer("latent_attention", _ket_latent(1, 10, 6, 6, 14, base=3000.0), ff=46),
+                    _ket_parallel(_ket_left(2, 1, 10, 6, 6, base=3000.0, softcap=5.0),
+                                  _ket_right(1, 10, 6, (0.95,)), ff=38)]}
+# wider, for bfloat16: a latent of 192 with 32 rotated sizes, delta-rule keys of 128 and of 160
+KET_D = {"architecture": "Ketopel", "vocab": 500, "width": 256, "norm": {"eps": 1e-5},
+         "embedding": {"scale": 4.0}, "loop": {"start": 1, "stop": 3, "times": 2},
+         "layers": [_ket_layer("latent_attention", _ket_latent(4, 64, 32, 64, 192), ff=512),
+                    _ket_layer("delta", _ket_delta(4, 2, 128, 64, 4), ff=384),
+                    _ket_parallel(_ket_left(8, 2, 64, 64, 32, scale=0.125, softcap=50.0,
+                                            scaling=(4.0, 256, 16.0, 1.0)),
+                                  _ket_right(4, 64, 32, (0.97, 0.99, 0.995, 0.999)), ls=0.8,
+                                  rs=0.9, ff=320),
+                    _ket_layer("delta", _ket_delta(2, 2, 160, 48, 2), ff=256)]}
+
+KET = {
+    "A": dict(raw=KET_A, std=0.08, norm_std=0.1, page_size=16, seed=25),
+    "B": dict(raw=KET_B, std=0.1, norm_std=0.1, page_size=4, seed=26),
+    "C": dict(raw=KET_C, std=0.12, norm_std=0.1, page_size=8, seed=27),
+    "D": dict(raw=KET_D, std=0.05, norm_std=0.05, page_size=16, seed=28),
+}
+
+
+def make_ketopel_dir(tmp_path, which, dtype=torch.float32, raw=None, tweak=None, tag="") -> str:
+    """A folder with config.json and random weights of a looped configuration; ``tweak(w)``
+    may change the tensors (a name -> tensor dictionary) before they are written."""
+    from binfer_b200.config import KetopelConfig
+    from binfer_b200.parts.model import param_specs_for
+    from binfer_b200.weights import random_tensors, save_file
+    t = KET[which]
+    raw = raw or t["raw"]
+    cfg = KetopelConfig.from_dict(raw)
+    d = os.path.join(str(tmp_path), f"ket_{which}{tag}_{str(dtype).split('.')[-1]}")
+    os.makedirs(d, exist_ok=True)
+    with open(os.path.join(d, "config.json"), "w") as f:
+        json.dump(cfg.to_dict(), f)
+    w = random_tensors(param_specs_for(cfg.to_spec()), t["seed"], t["std"], t["norm_std"], dtype)
+    if tweak is not None:
+        tweak(w)
+    save_file(w, os.path.join(d, "model.safetensors"))
+    return d
