@@ -294,6 +294,35 @@ def side_by_side_config(size, layers, window=1024, keep=4):
             "logit_scale": 1.0, "layers": [layer] * layers}
 
 
+def looped_config(size, layers=8):
+    """The looped design at the Qwen3 shape of that name, ``layers`` layer runs (at least 4):
+    latent attention first and last, between them a gated delta rule layer and a side-by-side
+    layer that are walked ``(layers - 2) / 2`` times.  The softmax branch has the shape's
+    heads; latent attention has as many heads, of 128 plain and 64 rotated sizes, over a
+    latent of 512; the delta rule has value heads of 128 that together are as wide as the
+    model and half as many key heads; lightning attention has eight heads of 128; the
+    feed-forward is the shape's."""
+    width, heads, kv, d, ff = HYBRID_SIZES[size][:5]
+    mlp = {"kind": "dense", "ff": ff}
+    latent = {"type": "latent_attention", "mlp": mlp,
+              "mixer": {"heads": heads, "dim": 128, "rot_dim": 64, "vdim": 128, "kv_rank": 512,
+                        "scale": 192 ** -0.5, "rot": {"base": 1e4, "dims": 64}}}
+    vh = width // 128
+    delta = {"type": "delta", "mlp": mlp,
+             "mixer": {"heads": vh, "kv_heads": vh // 2, "dim": 128, "vdim": 128, "conv": 4}}
+    left = {"heads": heads, "kv_heads": kv, "dim": d, "vdim": d, "scale": d ** -0.5,
+            "softcap": 30.0,
+            "rot": {"base": 1e6, "dims": d // 2,
+                    "scaling": {"factor": 4.0, "original": 4096, "fast": 32.0, "slow": 1.0}}}
+    right = {"heads": 8, "dim": 128, "vdim": 128,
+             "decay": [1.0 - 2.0 ** (-5 - 4.0 * i / 7) for i in range(8)]}
+    side = {"type": "parallel", "mlp": mlp,
+            "mixer": {"left": left, "right": right, "left_scale": 1.0, "right_scale": 1.0}}
+    return {"architecture": "Ketopel", "vocab": 32000, "width": width, "norm": {"eps": 1e-5},
+            "embedding": {"scale": 1.0}, "layers": [latent, delta, side, latent],
+            "loop": {"start": 1, "stop": 3, "times": max(1, (layers - 2) // 2)}}
+
+
 def hybrid_compare(args, design="hybrid"):
     """Prefill and decode throughput of the hybrid design (matrix-memory layers alternating
     with pooled-window attention layers), or with ``design`` "side_by_side" of the design
@@ -305,13 +334,14 @@ def hybrid_compare(args, design="hybrid"):
     (event pairs around every launch, eager).  Random weights, bfloat16."""
     import torch
     from binfer_b200 import Engine, Qwen3Config
-    from binfer_b200.config import FikotarConfig, GukidraConfig
+    from binfer_b200.config import FikotarConfig, GukidraConfig, KetopelConfig
     from binfer_b200.engine.runner import StepItem
     from binfer_b200.profiling import Profiler
     layers = args.layers or 8
     B, context, ps = args.batch or 8, 4096, args.page_size
     steps, warmup = min(args.steps, 64), max(args.warmup, 3)
-    what = {"hybrid": "hybrid design", "side_by_side": "side-by-side design"}[design]
+    what = {"hybrid": "hybrid design", "side_by_side": "side-by-side design",
+            "looped": "looped design"}[design]
     record = {"metric": what + " beside the Qwen3 decoder at equal layer sizes "
                         "(prefill of 2048 tokens; decode at batch %d, context %d)" % (B, context),
               "dtype": "bf16", "data": "synthetic", "layers": layers, "sizes": {}}
@@ -321,6 +351,7 @@ def hybrid_compare(args, design="hybrid"):
                     tie_word_embeddings=True)
         out = {}
         ours = (GukidraConfig.from_dict(hybrid_config(size, layers)) if design == "hybrid"
+                else KetopelConfig.from_dict(looped_config(size, layers)) if design == "looped"
                 else FikotarConfig.from_dict(side_by_side_config(size, layers)))
         for name, cfg in ((design, ours), ("qwen3", Qwen3Config.from_dict(qwen))):
             engine = Engine(cfg, "bfloat16", random_seed=0, num_pages=(B + 1) * (context // ps) + 64,
@@ -463,7 +494,11 @@ def main():
     ap.add_argument("--side-by-side", action="store_true",
                     help="the same for the design whose layers run convolved window attention "
                          "beside retention, with a mixture of experts")
-    ap.add_argument("--hybrid-sizes", default="", help="with --hybrid or --side-by-side: 1.7b, "
+    ap.add_argument("--looped", action="store_true",
+                    help="the same for the design whose layers (latent attention, the gated "
+                         "delta rule, whole-norm attention beside lightning attention) are "
+                         "partly walked several times")
+    ap.add_argument("--hybrid-sizes", default="", help="with --hybrid, --side-by-side or --looped: 1.7b, "
                                                        "8b or both (default)")
     args = ap.parse_args()
     if args.impl == "reference":
@@ -477,6 +512,8 @@ def main():
         return hybrid_compare(args)
     if args.side_by_side:
         return hybrid_compare(args, "side_by_side")
+    if args.looped:
+        return hybrid_compare(args, "looped")
     if args.profile:
         return profile_steps(args)
     if args.workload == "serve":

@@ -18,7 +18,8 @@
 // `keep_first` tokens (their tiles are walked between the blocks' and the window's, each
 // row masking what its window covers anyway), and a learned sink logit per query head
 // (`sinks`) in place of the constant one.  `q_stride`, `out_stride` and `out_scale` let q and
-// the result be column blocks of wider buffers, the result scaled.
+// the result be column blocks of wider buffers, the result scaled.  A soft cap c > 0 turns a
+// scaled score z into c tanh(z / c) before the mask and the softmax.
 //
 // Key and value head sizes: multiples of 16 up to 128; at most 64 query heads per kv head.
 #include <float.h>
@@ -136,7 +137,7 @@ __global__ void __launch_bounds__(PWM_THREADS) pwm_attention_kernel(
     int num_pages, int s_page_size, int s_num_pages, int window, int pool, float scale_log2,
     int has_sink, float sink_log2, float* __restrict__ part_o, float* __restrict__ part_ml,
     int* __restrict__ err, const float* __restrict__ sinks, int keep_first, long long q_stride,
-    long long out_stride, float out_scale) {
+    long long out_stride, float out_scale, float cap_pre, float cap_post) {
   extern __shared__ __align__(16) unsigned char smem_raw[];
   const int pitch_k = dk + 8, pitch_v = dv + 8;
   // two stages of (K tile, V tile); the first K tile's place holds the Q tile to begin with
@@ -278,6 +279,17 @@ __global__ void __launch_bounds__(PWM_THREADS) pwm_attention_kernel(
           pwm_mma(s[2 * np + 1], qf[ks], kb[2], kb[3]);
         }
       }
+    }
+    if (cap_pre > 0.f) {       // s <- (c / scale) tanh(s scale / c): the scale still rides below
+#pragma unroll
+      for (int n = 0; n < PWM_KEYS / 8; ++n)
+#pragma unroll
+        for (int e = 0; e < 4; ++e) {
+          // tanh z = 1 - 2 / (exp(2 z) + 1): right at both ends, where the power is 0 or inf
+          float t;
+          asm("ex2.approx.ftz.f32 %0, %1;" : "=f"(t) : "f"(s[n][e] * cap_pre));
+          s[n][e] = cap_post - __fdividef(2.f * cap_post, t + 1.f);
+        }
     }
     // Each row masks by its own position; a tile that every row of this warp sees whole (the
     // common case inside a window) skips the tests.  Scores stay unscaled: the scale rides on
@@ -579,7 +591,7 @@ BF_EXPORT int bf_pwm_attention(
     int max_tokens, int nh, int nkv, int dk, int dv, int page_size, int num_pages,
     int s_page_size, int s_num_pages, int window, int pool, float scale, int has_sink,
     float sink, float* part_o, float* part_ml, int shares, int* err, const float* sinks,
-    int keep_first, long long q_stride, long long out_stride, float out_scale,
+    int keep_first, long long q_stride, long long out_stride, float out_scale, float softcap,
     cudaStream_t stream) {
   // part_o [B, nkv, shares, 16, dv], part_ml [B, nkv, shares, 16, 2] (float, or null): scratch
   // for steps of single tokens, whose keys are then shared out over `shares` CTAs a row
@@ -613,7 +625,8 @@ BF_EXPORT int bf_pwm_attention(
       table_stride, s_tables, s_table_stride, (const __nv_bfloat16*)gate, gate_stride, v_inv_freq,
       interleaved, (__nv_bfloat16*)out, nh, nkv, dk, dv, page_size, num_pages, s_page_size,
       s_num_pages, window, pool, scale * log2e, has_sink, sink * log2e, part_o, part_ml, err,
-      sinks, keep_first, q_stride, out_stride, out_scale);
+      sinks, keep_first, q_stride, out_stride, out_scale,
+      softcap > 0.f ? 2.f * log2e * scale / softcap : 0.f, softcap > 0.f ? softcap / scale : 0.f);
   if (multi) {
     const int e = bf_launch_status();
     if (e) return e;

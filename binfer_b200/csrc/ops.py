@@ -972,7 +972,7 @@ def pwm_attention(q: torch.Tensor, k_cache: torch.Tensor, v_cache: torch.Tensor,
                   B: int, max_tokens: int, nh: int, nkv: int, dk: int, dv: int,
                   window: Optional[int], pool: int, scale: float, sink: Optional[float],
                   err: torch.Tensor, max_ctx: int = 0, sinks: Optional[torch.Tensor] = None,
-                  keep_first: int = 0, out_scale: float = 1.0) -> None:
+                  keep_first: int = 0, out_scale: float = 1.0, softcap: float = 0.0) -> None:
     """``apw_attention`` on the tensor cores (bfloat16; sizes: ``pwm_attention_takes``):
     request ``b`` of the batch owns the token rows ``q_start[b] .. q_start[b+1]-1``, at most
     ``max_tokens`` of them.  ``max_ctx``: the longest context in the batch, if the caller
@@ -981,7 +981,8 @@ def pwm_attention(q: torch.Tensor, k_cache: torch.Tensor, v_cache: torch.Tensor,
     ``sinks`` (float32 ``[nh]``): a learned logit per query head in the softmax's denominator
     instead of the constant ``sink``.  ``keep_first``: with a window, the request's first
     that many tokens stay visible behind it.  ``out`` may be a column block of a wider
-    buffer; ``out_scale`` multiplies the result."""
+    buffer; ``out_scale`` multiplies the result.  ``softcap`` c > 0: a scaled score z becomes
+    ``c tanh(z / c)``."""
     if not pwm_attention_takes(q.dtype, nh, nkv, dk, dv):
         raise KernelError("pwm_attention: bfloat16, head sizes multiples of 16 up to 128")
     if not q.is_contiguous() or out.stride(1) != 1 or q.data_ptr() % 16:
@@ -1019,7 +1020,57 @@ def pwm_attention(q: torch.Tensor, k_cache: torch.Tensor, v_cache: torch.Tensor,
          _c_int(window or 0), _c_int(pool if has_s else 0), _c_float(scale),
          _c_int(0 if sink is None and sinks is None else 1), _c_float(sink or 0.0),
          _ptr(part_o), _ptr(part_ml), _c_int(shares), _ptr(err), _ptr(sinks), _c_int(keep_first),
-         _c_ll(q.stride(0)), _c_ll(out.stride(0)), _c_float(out_scale), _stream())
+         _c_ll(q.stride(0)), _c_ll(out.stride(0)), _c_float(out_scale), _c_float(softcap),
+         _stream())
+
+
+def latent_attention_takes(dtype: torch.dtype, rank: int, rot: int) -> bool:
+    """Whether the tensor-core kernel of the attention over a cached latent takes these
+    sizes."""
+    return (dtype == torch.bfloat16 and rank % 16 == 0 and rot % 16 == 0 and 0 < rank <= 512
+            and rank + rot <= 640)
+
+
+LATENT_ROWS, LATENT_KEYS = 32, 64
+
+
+def latent_attention(q: torch.Tensor, cache: torch.Tensor, q_start: torch.Tensor,
+                     positions: torch.Tensor, tables: torch.Tensor, out: torch.Tensor, B: int,
+                     max_tokens: int, H: int, rank: int, scale: float, err: torch.Tensor,
+                     max_ctx: int = 0) -> None:
+    """Causal softmax attention of query rows ``q [T, H, W]`` (already in the latent's
+    coordinates) over a cache of one row ``[latent (rank) | shared key part]`` of ``W`` numbers
+    per token, whose first ``rank`` numbers are also the value: ``out [T, H, rank]``, on the
+    tensor cores (bfloat16; sizes: ``latent_attention_takes``).  Request ``b`` owns the token
+    rows ``q_start[b] .. q_start[b+1]-1``, at most ``max_tokens`` of them.  ``max_ctx``: the
+    longest context in the batch, if the caller knows it: a step with few rows then shares
+    each request's key tiles out over several CTAs whose partial results a second kernel
+    makes one."""
+    W = q.shape[-1]
+    if not latent_attention_takes(q.dtype, rank, W - rank):
+        raise KernelError("latent_attention: bfloat16, a latent of a multiple of 16 up to 512, "
+                          "with the shared part at most 640")
+    if not q.is_contiguous() or not out.is_contiguous() or cache.shape[1] != 1 or cache.shape[3] != W:
+        raise KernelError("latent_attention: q and out must be contiguous, the cache one head "
+                          "of q's width per token")
+    max_rows = max_tokens * H
+    tiles = (max_rows + LATENT_ROWS - 1) // LATENT_ROWS
+    part_o = part_ml = None
+    splits = 1
+    if max_ctx > 0:
+        key_tiles = (max_ctx + LATENT_KEYS - 1) // LATENT_KEYS
+        room = num_sms(q.device) // max(1, tiles * B)
+        splits = max(1, min(room, (key_tiles + 1) // 2, 32))
+        if splits > 1:
+            part_o = torch.empty((B, tiles, splits, LATENT_ROWS, rank), dtype=torch.float32,
+                                 device=q.device)
+            part_ml = torch.empty((B, tiles, splits, LATENT_ROWS, 2), dtype=torch.float32,
+                                  device=q.device)
+    _run("latent_attention", lib().bf_latent_attention, _ptr(q), _ptr(cache), _ptr(q_start),
+         _ptr(positions), _ptr(tables), _c_int(tables.stride(0)), _ptr(out), _c_int(B),
+         _c_int(max_rows), _c_int(H), _c_int(W), _c_int(rank), _c_int(cache.shape[2]),
+         _c_int(cache.shape[0]), _c_float(scale), _ptr(part_o), _ptr(part_ml), _c_int(splits),
+         _ptr(err), _stream())
 
 
 # ------------------------------------------------------------- matrix products

@@ -145,7 +145,7 @@ class ConvWindowAttention(Mixer):
         if self.taps > 1:
             ops.conv_state_shift(proj, state, ctx.state_slots, ctx.q_start, ctx.B, self.taps)
         keep = s.keep_first if s.window is not None else 0
-        if (TENSOR_CORES and s.softmax_scale > 0 and not s.softcap
+        if (TENSOR_CORES and s.softmax_scale > 0
                 and ops.pwm_attention_takes(proj.dtype, self.H, self.G, self.dk, self.dv)):
             # bfloat16: tiles of (token, head of a group) rows on the tensor cores, prompt
             # portions and single tokens alike (the windowed kernel, without pooled blocks)
@@ -154,7 +154,7 @@ class ConvWindowAttention(Mixer):
                               ctx.B, 1 if ctx.decode_only else ctx.max_q_len, self.H, self.G,
                               self.dk, self.dv, s.window, 0, s.softmax_scale, None, ctx.err,
                               max_ctx=ctx.max_ctx_len, sinks=self.sinks, keep_first=keep,
-                              out_scale=out_scale)
+                              out_scale=out_scale, softcap=s.softcap)
             return
         ops.paged_attention_generic(
             q, view.k_cache, view.v_cache, ctx.seq_of_token, ctx.positions, ctx.block_tables[g],

@@ -18,6 +18,7 @@ portions and single tokens alike, so the logits cannot depend on how a prompt wa
 from __future__ import annotations
 
 import dataclasses
+import os
 from typing import Callable, List, Optional
 
 import torch
@@ -28,6 +29,10 @@ from ..csrc import ops
 from ..weights.loader import ParamSpec
 from .base import BuildEnv, EntryView, Mixer, StepContext, build_position, register_mixer
 from .linear import linear, linear_heads
+
+# BINFER_B200_LATENT_TENSOR_CORES=0: the one-warp-per-row kernel also in bfloat16 (the float32
+# path), to tell the two apart when something differs
+TENSOR_CORES = os.environ.get("BINFER_B200_LATENT_TENSOR_CORES", "1") != "0"
 
 
 class LatentAttention(Mixer):
@@ -104,10 +109,20 @@ class LatentAttention(Mixer):
         q_heads = proj[:, :self.q_size].view(T, H, self.d + self.dr)
         linear_heads(q_heads[:, :, :self.d], self.w_ukT, q_abs[:, :, :self.rank])
         o_lat = torch.empty((T, H, self.rank), dtype=x.dtype, device=x.device)
-        ops.paged_attention_generic(
-            q_abs.view(T, H * self.kv_size), view.k_cache, view.k_cache, ctx.seq_of_token,
-            ctx.positions, ctx.block_tables[g], o_lat.view(T, H * self.rank), H, 1, self.kv_size,
-            None, s.softmax_scale, ctx.err, value_dim=self.rank, v_stride=self.kv_size)
+        if (TENSOR_CORES and s.softmax_scale > 0
+                and ops.latent_attention_takes(x.dtype, self.rank, self.dr)):
+            # bfloat16: tiles of (token, head) rows against tiles of cache rows, each fetched
+            # once as keys and values, on the tensor cores
+            ops.latent_attention(q_abs, view.k_cache, ctx.q_start, ctx.positions,
+                                 ctx.block_tables[g], o_lat, ctx.B,
+                                 1 if ctx.decode_only else ctx.max_q_len, H, self.rank,
+                                 s.softmax_scale, ctx.err, max_ctx=ctx.max_ctx_len)
+        else:
+            ops.paged_attention_generic(
+                q_abs.view(T, H * self.kv_size), view.k_cache, view.k_cache, ctx.seq_of_token,
+                ctx.positions, ctx.block_tables[g], o_lat.view(T, H * self.rank), H, 1,
+                self.kv_size, None, s.softmax_scale, ctx.err, value_dim=self.rank,
+                v_stride=self.kv_size)
         out = torch.empty((T, H, self.dv), dtype=x.dtype, device=x.device)
         linear_heads(o_lat, self.w_uv, out)
         out = out.view(T, H * self.dv)

@@ -296,6 +296,118 @@ def test_latent_attention_sizes(cuda_device, tmp_path, heads, d, dr, dv, rank):
         _compare(got, ref, torch.float32, f"latent {heads}x{d}+{dr}/{rank}/{name}")
 
 
+def _latent_attention_plain(q, rows, rank, scale, pos):
+    """One token's heads ``q [H, W]`` over the cache rows ``rows [n, W]`` of its request, of
+    which it sees ``0 .. pos``: softmax(scale q K^T) V with V the rows' first ``rank``."""
+    keys = rows[:pos + 1].double()
+    w = torch.softmax(q.double() @ keys.T * scale, dim=-1)
+    return (w @ keys[:, :rank]).float()
+
+
+@pytest.mark.parametrize("H_,rank,rot,ps", [(16, 512, 64, 16), (3, 16, 0, 8), (5, 192, 32, 64),
+                                            (40, 48, 128, 16), (1, 512, 128, 32)])
+def test_latent_attention_kernel_on_the_tensor_cores(cuda_device, H_, rank, rot, ps):
+    """The kernel alone in bfloat16 against float arithmetic on the same rounded numbers:
+    whole prompts, later portions (down to two tokens, starting inside a key tile and a page)
+    and single tokens of unequal requests in one batch, over pages in a shuffled order, and a
+    step of single tokens whose key tiles are shared out over CTAs (with the longest context
+    given larger than it is, as a captured step has it)."""
+    from binfer_b200.csrc import ops
+    dev, W = cuda_device, rank + rot
+    gen = torch.Generator().manual_seed(H_ * 1000 + rank)
+    # (context before the step, tokens of the step)
+    batches = [[(0, 70), (64, 2), (33, 130), (199, 1), (0, 1)], [(300, 1), (63, 1), (0, 1), (129, 1)],
+               [(0, 257)], [(515, 1)]]
+    scale = 1.7 * W ** -0.5
+    for bi, reqs in enumerate(batches):
+        pages_of = [(c + n + ps - 1) // ps for c, n in reqs]
+        total = sum(pages_of)
+        order = torch.randperm(total, generator=gen)
+        cache = torch.zeros((total + 1, 1, ps, W), dtype=torch.bfloat16)
+        tables = torch.full((len(reqs), max(pages_of)), -1, dtype=torch.int32)
+        qs, positions, q_start, refs, at = [], [], [0], [], 0
+        for b, (c, n) in enumerate(reqs):
+            rows = (torch.randn((c + n, W), generator=gen) * 0.8).to(torch.bfloat16)
+            mine = order[at:at + pages_of[b]]
+            at += pages_of[b]
+            tables[b, :pages_of[b]] = mine.to(torch.int32)
+            for j in range(c + n):
+                cache[mine[j // ps], 0, j % ps] = rows[j]
+            q = (torch.randn((n, H_, W), generator=gen) * 1.5).to(torch.bfloat16)
+            qs.append(q)
+            positions += list(range(c, c + n))
+            q_start.append(q_start[-1] + n)
+            refs += [_latent_attention_plain(q[i].float(), rows.float(), rank, scale, c + i)
+                     for i in range(n)]
+        q = torch.cat(qs).to(dev)
+        ref = torch.stack(refs)
+        out = torch.full((q.shape[0], H_, rank), float("nan"), dtype=torch.bfloat16, device=dev)
+        err = ops.error_word(dev)
+        single = all(n == 1 for _, n in reqs)
+        longest = max(c + n for c, n in reqs)
+        for max_ctx in ([0, longest, longest + 700] if single else [0, longest]):
+            out.fill_(float("nan"))
+            ops.latent_attention(q, cache.to(dev), torch.tensor(q_start, dtype=torch.int32, device=dev),
+                                 torch.tensor(positions, dtype=torch.int32, device=dev),
+                                 tables.to(dev), out, len(reqs), max(n for _, n in reqs), H_, rank,
+                                 scale, err, max_ctx=max_ctx)
+            assert int(err.item()) == 0
+            e = H.rel_err(out.float().cpu(), ref)
+            assert e <= 1.2e-2, f"batch {bi}, longest context given as {max_ctx}: {e:.3g}"
+
+
+@pytest.mark.parametrize("case", sorted(EDGES))
+@pytest.mark.parametrize("which", ["whole_norm", "latent"])
+def test_attention_at_its_edges_on_the_tensor_cores(cuda_device, tmp_path, which, case):
+    """The marked keys again, in bfloat16 and with sizes that the tensor-core kernels take (the
+    soft cap among them); the profiler shows that those kernels ran."""
+    from binfer_b200.csrc import ops
+    from binfer_b200.profiling import Profiler
+    if which == "whole_norm":
+        left = H._ket_left(4, 2, 32, 16, 16, scale=0.6, softcap=25.0, scaling=(4.0, 32, 8.0, 1.0))
+        raw = _one_layer(H._ket_parallel(left, H._ket_right(1, 8, 8, (0.9,)), ls=1.3, rs=0.0),
+                         vocab=400, width=64)
+        from binfer_b200.parts import attention_conv_window as mod
+        tweak_of, kernel = _stand_out_left, "pwm_attention"
+    else:
+        raw = _one_layer(H._ket_layer("latent_attention", H._ket_latent(3, 24, 16, 20, 32, scale=0.3),
+                                      ff=56), vocab=400, width=64)
+        from binfer_b200.parts import attention_latent as mod
+        tweak_of, kernel = _stand_out_latent, "latent_attention"
+    key, query = EDGES[case]
+    toks = _distinct_tokens(240, raw["vocab"], 21)
+    d = H.make_ketopel_dir(tmp_path, "A", torch.bfloat16, raw=raw,
+                           tweak=tweak_of(raw, toks, (key, query), boost=12.0), tag=which + case)
+    raw, w = H.read_model_dir(d)
+    ref = {"a": P.forward(raw, w, toks)}
+    other = list(toks)
+    other[key] = next(t for t in range(raw["vocab"]) if t not in toks)
+    moved = H.rel_err(P.forward(raw, w, other)[query], ref["a"][query])
+    assert moved > 0.5, f"{case}: the key moves the logits by {moved:.3g} only"
+    # a model this narrow is rounded coarsely in bfloat16 whatever the kernel: the kernel for
+    # any sizes on the same rounded numbers is the sharp comparison
+    outs = []
+    for on in (True, False):
+        mod.TENSOR_CORES = on
+        seen, got = set(), {}
+        try:
+            for name, steps in _all_regimes({"a": toks}, tail=100).items():
+                prof = Profiler()
+                got[name] = H.run_trace(_runner(d, torch.bfloat16, 8, H.peak_pages(steps, 8)), steps)
+                prof.stop()
+                seen |= set(prof.collect())
+                worst = max(H.rel_err(row, ref[rid][pos]) for (rid, pos), row in got[name].items())
+                assert worst <= 0.16, f"{which}/{case}/{name} (tensor cores {on}): {worst:.3g}"
+        finally:
+            ops.set_profiler(None)
+            mod.TENSOR_CORES = True
+        assert (kernel in seen) == on and ("paged_attention_generic" in seen) != on, sorted(seen)
+        outs.append(got)
+    for name in outs[0]:
+        worst = max(H.rel_err(outs[0][name][k], outs[1][name][k]) for k in outs[0][name])
+        assert worst <= 0.03, f"{which}/{case}/{name}: the two kernels differ by {worst:.3g}"
+
+
 def test_soft_cap_and_stretched_waves_count(cuda_device, tmp_path):
     """The plain implementation first shows that leaving out the cap, the stretching or the
     larger cosines moves the logits; the engine is then held to the full form."""
