@@ -10,15 +10,31 @@
 // can be cut anywhere.
 //
 // A block owns `cols` output columns of one (request, head); a column is shared by KS
-// adjacent lanes that each hold R consecutive state elements of it in registers.  Up to
-// `stage` tokens' q, k, v and gates are staged in shared memory at a time.  Per token a lane
-// forms its share of S^T k with the state as it was (the decay multiplies the sum, not the
-// elements), the KS shares are added by shuffles, and one pass then updates the state,
-// S <- g S + k u^T, and forms the lane's share of S^T q.  Every sum has an order that depends
-// on the sizes alone, so the result does not depend on how the tokens were cut into steps.
+// adjacent lanes.  A lane holds R state elements of its column in registers, in pieces of
+// four that lie KS pieces apart (piece r4 of lane `part` is piece r4 KS + part of the
+// column), so that the lanes of a column read neighbouring 16-byte pieces of a token's k and
+// q from shared memory (no bank conflicts) and of the state from the slot (whole lines).
+//
+// The chain from token to token is kept short.  Both S^T k and S^T q are formed from the
+// state as the token before left it, side by side and added over the KS lanes by one round of
+// shuffles; with g the decay and u as above, the read-out of the state after the write is
+//
+//   o_t = g (S_old^T q_t) + (k_t . q_t) u_t,
+//
+// and the state's update S <- g S + k u^T then waits for u alone.  k_t . q_t, and the
+// token's k, q and v themselves, are fetched and formed one token ahead, under the chain of
+// the token before.  Up to `stage` tokens are staged in shared memory at a time, in two
+// buffers: the next stage's asynchronous copies travel while this one is walked.  Every sum
+// has an order that depends on the sizes alone, so the result does not depend on how the
+// tokens were cut into steps.
 #include "common.cuh"
 
 #define DR_THREADS 128
+
+__device__ __forceinline__ void dr_cp16(float* smem, const float* gmem) {
+  const uint32_t sa = (uint32_t)__cvta_generic_to_shared(smem);
+  asm volatile("cp.async.cg.shared.global [%0], [%1], 16;" ::"r"(sa), "l"(gmem));
+}
 
 template <int R>
 __global__ void __launch_bounds__(DR_THREADS) delta_scan_kernel(
@@ -27,8 +43,9 @@ __global__ void __launch_bounds__(DR_THREADS) delta_scan_kernel(
     int n_slots, float* __restrict__ o_raw, int H, int G, int dk, int dv, int KS, int stage,
     int* __restrict__ err) {
   extern __shared__ __align__(16) float sh[];
+  constexpr int R4 = R / 4;
   const int cols = DR_THREADS / KS;
-  const int dkp = KS * R;
+  const int dkp = KS * R;                   // dk rounded up to what the lanes of a column hold
   const int b = blockIdx.z, h = blockIdx.y, col0 = blockIdx.x * cols;
   const int g = h / (H / G);
   const int tid = threadIdx.x;
@@ -42,68 +59,158 @@ __global__ void __launch_bounds__(DR_THREADS) delta_scan_kernel(
     return;
   }
   const int C = 2 * G * dk + H * dv;
-  float* sp = state + (size_t)slot * state_stride + ((size_t)h * dv + col) * dk + (size_t)part * R;
+  float* sp = state + (size_t)slot * state_stride + ((size_t)h * dv + col) * dk;
+  // whole pieces of four floats where the sizes and the slot's address allow it
+  const bool st16 = (dk & 3) == 0 && (state_stride & 3) == 0 && (((uintptr_t)state) & 15) == 0;
   float S[R];
 #pragma unroll
-  for (int r = 0; r < R; ++r) S[r] = (col < dv && part * R + r < dk) ? sp[r] : 0.f;
+  for (int r4 = 0; r4 < R4; ++r4) {
+    const int i = (r4 * KS + part) * 4;
+    if (st16 && col < dv && i < dk) {
+      const float4 x = *reinterpret_cast<const float4*>(sp + i);
+      S[4 * r4] = x.x; S[4 * r4 + 1] = x.y; S[4 * r4 + 2] = x.z; S[4 * r4 + 3] = x.w;
+    } else {
+#pragma unroll
+      for (int e = 0; e < 4; ++e) S[4 * r4 + e] = (col < dv && i + e < dk) ? sp[i + e] : 0.f;
+    }
+  }
 
-  float* qs = sh;                         // [stage][dkp]
-  float* ks = qs + (size_t)stage * dkp;   // [stage][dkp]
-  float* vs = ks + (size_t)stage * dkp;   // [stage][cols]
-  float* gs = vs + (size_t)stage * cols;  // [stage][2]: beta, decay
-  for (int s0 = 0; s0 < n; s0 += stage) {
+  // one buffer: [stage][dkp] q, [stage][dkp] k, [stage][cols] v, [stage][2] beta and decay
+  const int buf_elems = stage * (2 * dkp + cols + 2);
+  const bool rows16 = (dk & 3) == 0 && (C & 3) == 0;
+  auto issue = [&](int s0, int buf) {
     const int sn = min(stage, n - s0);
-    __syncthreads();                      // the stage before is used up
-    for (int idx = tid; idx < sn * dkp; idx += DR_THREADS) {
-      const int c = idx / dkp, i = idx - c * dkp;
-      const float* row = qkv + (size_t)(t0 + s0 + c) * C + (size_t)g * dk;
-      qs[idx] = i < dk ? row[i] : 0.f;
-      ks[idx] = i < dk ? row[(size_t)G * dk + i] : 0.f;
+    float* qd = sh + (size_t)buf * buf_elems;
+    float* kd = qd + stage * dkp;
+    float* vd = kd + stage * dkp;
+    float* gd = vd + stage * cols;
+    if (rows16) {
+      const int d4 = dkp >> 2, have = dk >> 2;
+      for (int idx = tid; idx < sn * d4; idx += DR_THREADS) {
+        const int c = idx / d4, i = idx - c * d4;
+        if (i < have) {
+          const float* row = qkv + (size_t)(t0 + s0 + c) * C + (size_t)g * dk + 4 * i;
+          dr_cp16(qd + 4 * idx, row);
+          dr_cp16(kd + 4 * idx, row + (size_t)G * dk);
+        } else {
+          *reinterpret_cast<float4*>(qd + 4 * idx) = make_float4(0.f, 0.f, 0.f, 0.f);
+          *reinterpret_cast<float4*>(kd + 4 * idx) = make_float4(0.f, 0.f, 0.f, 0.f);
+        }
+      }
+    } else {
+      for (int idx = tid; idx < sn * dkp; idx += DR_THREADS) {
+        const int c = idx / dkp, i = idx - c * dkp;
+        const float* row = qkv + (size_t)(t0 + s0 + c) * C + (size_t)g * dk;
+        qd[idx] = i < dk ? row[i] : 0.f;
+        kd[idx] = i < dk ? row[(size_t)G * dk + i] : 0.f;
+      }
     }
     for (int idx = tid; idx < sn * cols; idx += DR_THREADS) {
       const int c = idx / cols, j = idx - c * cols;
-      vs[idx] = col0 + j < dv
+      vd[idx] = col0 + j < dv
                     ? qkv[(size_t)(t0 + s0 + c) * C + 2 * (size_t)G * dk + (size_t)h * dv + col0 + j]
                     : 0.f;
     }
     for (int idx = tid; idx < sn * 2; idx += DR_THREADS) {
       const int c = idx >> 1, w = idx & 1;
-      gs[idx] = gates[((size_t)(t0 + s0 + c) * 2 + w) * H + h];
+      gd[idx] = gates[((size_t)(t0 + s0 + c) * 2 + w) * H + h];
+    }
+    asm volatile("cp.async.commit_group;" ::);
+  };
+  issue(0, 0);
+  int buf = 0;
+  for (int s0 = 0; s0 < n; s0 += stage, buf ^= 1) {
+    const int sn = min(stage, n - s0);
+    if (s0 + stage < n) {                   // the next stage travels while this one is used
+      issue(s0 + stage, buf ^ 1);
+      asm volatile("cp.async.wait_group 1;" ::);
+    } else {
+      asm volatile("cp.async.wait_group 0;" ::);
     }
     __syncthreads();
-    for (int c = 0; c < sn; ++c) {
-      const float* kr = ks + (size_t)c * dkp + part * R;
-      const float* qr = qs + (size_t)c * dkp + part * R;
-      const float beta = gs[2 * c], decay = gs[2 * c + 1];
-      float kk[R];
-      float a0 = 0.f, a1 = 0.f;
-#pragma unroll
-      for (int r = 0; r < R; r += 2) {
-        kk[r] = kr[r];
-        kk[r + 1] = kr[r + 1];
-        a0 = fmaf(S[r], kk[r], a0);
-        a1 = fmaf(S[r + 1], kk[r + 1], a1);
-      }
-      float sk = a0 + a1;
-      for (int o = 1; o < KS; o <<= 1) sk += __shfl_xor_sync(0xffffffffu, sk, o);
-      const float u = beta * (vs[c * cols + cg] - decay * sk);
-      a0 = a1 = 0.f;
-#pragma unroll
-      for (int r = 0; r < R; r += 2) {
-        S[r] = fmaf(decay, S[r], kk[r] * u);
-        S[r + 1] = fmaf(decay, S[r + 1], kk[r + 1] * u);
-        a0 = fmaf(S[r], qr[r], a0);
-        a1 = fmaf(S[r + 1], qr[r + 1], a1);
-      }
-      float so = a0 + a1;
-      for (int o = 1; o < KS; o <<= 1) so += __shfl_xor_sync(0xffffffffu, so, o);
-      if (part == 0 && col < dv)
-        o_raw[(size_t)(t0 + s0 + c) * H * dv + (size_t)h * dv + col] = so;
+    const float* qs = sh + (size_t)buf * buf_elems;
+    const float* ks = qs + stage * dkp;
+    const float* vs = ks + stage * dkp;
+    const float* gs = vs + stage * cols;
+    // a token's k, q, v, gates and k . q, held one token ahead in two sets of registers
+    float4 kk[2][R4], qq[2][R4];
+    float vv[2], be[2], de[2], kq[2];
+#define DR_FETCH(c, bi)                                                                  \
+  {                                                                                     \
+    const float4* kr = reinterpret_cast<const float4*>(ks + (size_t)(c) * dkp) + part;  \
+    const float4* qr = reinterpret_cast<const float4*>(qs + (size_t)(c) * dkp) + part;  \
+    float d0 = 0.f, d1 = 0.f;                                                           \
+    _Pragma("unroll") for (int r4 = 0; r4 < R4; ++r4) {                                 \
+      kk[bi][r4] = kr[r4 * KS];                                                         \
+      qq[bi][r4] = qr[r4 * KS];                                                         \
+      d0 = fmaf(kk[bi][r4].x, qq[bi][r4].x, d0);                                        \
+      d1 = fmaf(kk[bi][r4].y, qq[bi][r4].y, d1);                                        \
+      d0 = fmaf(kk[bi][r4].z, qq[bi][r4].z, d0);                                        \
+      d1 = fmaf(kk[bi][r4].w, qq[bi][r4].w, d1);                                        \
+    }                                                                                   \
+    float d = d0 + d1;                                                                  \
+    for (int o = 1; o < KS; o <<= 1) d += __shfl_xor_sync(0xffffffffu, d, o);           \
+    kq[bi] = d;                                                                         \
+    vv[bi] = vs[(c) * cols + cg];                                                       \
+    be[bi] = gs[2 * (c)];                                                               \
+    de[bi] = gs[2 * (c) + 1];                                                           \
+  }
+#define DR_TOKEN(c, bi)                                                                  \
+  {                                                                                     \
+    float a0 = 0.f, a1 = 0.f, a2 = 0.f, a3 = 0.f, b0 = 0.f, b1 = 0.f, b2 = 0.f, b3 = 0.f; \
+    _Pragma("unroll") for (int r4 = 0; r4 < R4; ++r4) {                                 \
+      a0 = fmaf(S[4 * r4], kk[bi][r4].x, a0);                                           \
+      a1 = fmaf(S[4 * r4 + 1], kk[bi][r4].y, a1);                                       \
+      a2 = fmaf(S[4 * r4 + 2], kk[bi][r4].z, a2);                                       \
+      a3 = fmaf(S[4 * r4 + 3], kk[bi][r4].w, a3);                                       \
+      b0 = fmaf(S[4 * r4], qq[bi][r4].x, b0);                                           \
+      b1 = fmaf(S[4 * r4 + 1], qq[bi][r4].y, b1);                                       \
+      b2 = fmaf(S[4 * r4 + 2], qq[bi][r4].z, b2);                                       \
+      b3 = fmaf(S[4 * r4 + 3], qq[bi][r4].w, b3);                                       \
+    }                                                                                   \
+    float sk = (a0 + a1) + (a2 + a3), sq = (b0 + b1) + (b2 + b3);                       \
+    const float decay = de[bi];                                                         \
+    _Pragma("unroll") for (int r = 0; r < R; ++r) S[r] *= decay;                        \
+    for (int o = 1; o < KS; o <<= 1) {                                                  \
+      sk += __shfl_xor_sync(0xffffffffu, sk, o);                                        \
+      sq += __shfl_xor_sync(0xffffffffu, sq, o);                                        \
+    }                                                                                   \
+    const float u = be[bi] * (vv[bi] - decay * sk);                                     \
+    _Pragma("unroll") for (int r4 = 0; r4 < R4; ++r4) {                                 \
+      S[4 * r4] = fmaf(kk[bi][r4].x, u, S[4 * r4]);                                     \
+      S[4 * r4 + 1] = fmaf(kk[bi][r4].y, u, S[4 * r4 + 1]);                             \
+      S[4 * r4 + 2] = fmaf(kk[bi][r4].z, u, S[4 * r4 + 2]);                             \
+      S[4 * r4 + 3] = fmaf(kk[bi][r4].w, u, S[4 * r4 + 3]);                             \
+    }                                                                                   \
+    if (part == 0 && col < dv)                                                          \
+      o_raw[(size_t)(t0 + s0 + (c)) * H * dv + (size_t)h * dv + col] =                  \
+          fmaf(decay, sq, kq[bi] * u);                                                  \
+  }
+    DR_FETCH(0, 0)
+    int c = 0;
+    for (; c + 1 < sn; c += 2) {
+      DR_FETCH(c + 1, 1)
+      DR_TOKEN(c, 0)
+      if (c + 2 < sn) DR_FETCH(c + 2, 0)
+      DR_TOKEN(c + 1, 1)
     }
+    if (c < sn) DR_TOKEN(c, 0)
+#undef DR_FETCH
+#undef DR_TOKEN
+    __syncthreads();                        // this buffer is filled again in the next round
   }
 #pragma unroll
-  for (int r = 0; r < R; ++r)
-    if (col < dv && part * R + r < dk) sp[r] = S[r];
+  for (int r4 = 0; r4 < R4; ++r4) {
+    const int i = (r4 * KS + part) * 4;
+    if (st16 && col < dv && i < dk) {
+      *reinterpret_cast<float4*>(sp + i) =
+          make_float4(S[4 * r4], S[4 * r4 + 1], S[4 * r4 + 2], S[4 * r4 + 3]);
+    } else {
+#pragma unroll
+      for (int e = 0; e < 4; ++e)
+        if (col < dv && i + e < dk) sp[i + e] = S[4 * r4 + e];
+    }
+  }
 }
 
 BF_EXPORT int bf_delta_scan(const float* qkv, const float* gates, float* state,
@@ -116,19 +223,22 @@ BF_EXPORT int bf_delta_scan(const float* qkv, const float* gates, float* state,
   int KS = 1;
   while (KS * R < dk) KS <<= 1;
   const int cols = DR_THREADS / KS;
+  const size_t per_token = (size_t)(2 * KS * R + cols + 2) * sizeof(float);
   int stage = 32;
-  while (stage > 1 && stage / 2 >= max_q) stage >>= 1;
-  while (stage > 1 && (size_t)stage * (2 * KS * R + cols + 2) * sizeof(float) > 40 * 1024)
-    stage >>= 1;
-  const size_t smem = (size_t)stage * (2 * KS * R + cols + 2) * sizeof(float);
+  while (stage > 2 && stage / 2 >= max_q) stage >>= 1;
+  while (stage > 2 && 2 * stage * per_token > 64 * 1024) stage >>= 1;
+  const size_t smem = 2 * stage * per_token;
   dim3 grid((dv + cols - 1) / cols, H, B);
-  if (R == 16)
-    delta_scan_kernel<16><<<grid, DR_THREADS, smem, stream>>>(
-        qkv, gates, state, state_stride, q_start, state_slots, n_slots, o_raw, H, G, dk, dv, KS,
-        stage, err);
-  else
-    delta_scan_kernel<32><<<grid, DR_THREADS, smem, stream>>>(
-        qkv, gates, state, state_stride, q_start, state_slots, n_slots, o_raw, H, G, dk, dv, KS,
-        stage, err);
+#define DR_GO(RR)                                                                              \
+  {                                                                                            \
+    if (smem > 48 * 1024)                                                                      \
+      cudaFuncSetAttribute(delta_scan_kernel<RR>, cudaFuncAttributeMaxDynamicSharedMemorySize, \
+                           (int)smem);                                                         \
+    delta_scan_kernel<RR><<<grid, DR_THREADS, smem, stream>>>(                                 \
+        qkv, gates, state, state_stride, q_start, state_slots, n_slots, o_raw, H, G, dk, dv,   \
+        KS, stage, err);                                                                       \
+  }
+  if (R == 16) DR_GO(16) else DR_GO(32)
+#undef DR_GO
   return bf_launch_status();
 }
