@@ -541,15 +541,16 @@ KET_C = {"architecture": "Ketopel", "vocab": 131, "width": 50, "norm": {"eps": 1
                     _ket_layer("latent_attention", _ket_latent(1, 10, 6, 6, 14, base=3000.0), ff=46),
                     _ket_parallel(_ket_left(2, 1, 10, 6, 6, base=3000.0, softcap=5.0),
                                   _ket_right(1, 10, 6, (0.95,)), ff=38)]}
-# wider, for bfloat16: a latent of 192 with 32 rotated sizes, delta-rule keys of 128 and of 160
-KET_D = {"architecture": "Ketopel", "vocab": 500, "width": 256, "norm": {"eps": 1e-5},
-         "embedding": {"scale": 4.0}, "loop": {"start": 1, "stop": 3, "times": 2},
+# wider, for bfloat16: a latent of 192 with 32 rotated sizes, delta-rule keys of 128 and of 160;
+# the loop walks the two delta rule layers at the end
+KET_D = {"architecture": "Ketopel", "vocab": 500, "width": 192, "norm": {"eps": 1e-5},
+         "embedding": {"scale": 4.0}, "loop": {"start": 2, "stop": 4, "times": 2},
          "layers": [_ket_layer("latent_attention", _ket_latent(4, 64, 32, 64, 192), ff=512),
-                    _ket_layer("delta", _ket_delta(4, 2, 128, 64, 4), ff=384),
-                    _ket_parallel(_ket_left(8, 2, 64, 64, 32, scale=0.125, softcap=50.0,
+                    _ket_parallel(_ket_left(8, 4, 64, 32, 32, scale=0.11, softcap=50.0,
                                             scaling=(4.0, 256, 16.0, 1.0)),
                                   _ket_right(4, 64, 32, (0.97, 0.99, 0.995, 0.999)), ls=0.8,
                                   rs=0.9, ff=320),
+                    _ket_layer("delta", _ket_delta(4, 2, 128, 64, 4), ff=384),
                     _ket_layer("delta", _ket_delta(2, 2, 160, 48, 2), ff=256)]}
 
 KET = {
