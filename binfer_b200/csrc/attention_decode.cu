@@ -262,7 +262,7 @@ __global__ void __launch_bounds__(128)
 decode_attention_merge_kernel(const float* __restrict__ part_o, const float* __restrict__ part_ml,
                               const int* __restrict__ rows, const int* __restrict__ positions,
                               __nv_bfloat16* __restrict__ out, int nh, int window,
-                              int max_splits) {
+                              int max_splits, long long out_stride, float out_scale) {
   BF_TRACE_POINT(10 * BF_TR_MERGE);
   bf_pdl_trigger();
   bf_pdl_wait();
@@ -338,12 +338,12 @@ decode_attention_merge_kernel(const float* __restrict__ part_o, const float* __r
     acc.w += __shfl_xor_sync(0xffffffffu, acc.w, d);
   }
   if (sc == 0) {
-    const float inv = n > 0 ? 1.f / L : 0.f;
+    const float inv = n > 0 ? out_scale / L : 0.f;
     uint2 packed;
     __nv_bfloat162* o2 = reinterpret_cast<__nv_bfloat162*>(&packed);
     o2[0] = __floats2bfloat162_rn(acc.x * inv, acc.y * inv);
     o2[1] = __floats2bfloat162_rn(acc.z * inv, acc.w * inv);
-    *reinterpret_cast<uint2*>(out + ((size_t)t * nh + h) * D + cb + cg * 4) = packed;
+    *reinterpret_cast<uint2*>(out + (size_t)t * out_stride + (size_t)h * D + cb + cg * 4) = packed;
   }
 }
 
@@ -376,10 +376,12 @@ static int launch_decode(const void* q, const void* k_cache, const void* v_cache
   if (e) return e;
   if (n_rows * nh <= MERGE_FEW_PAIRS && max_splits >= MERGE_MANY_SPLITS)
     decode_attention_merge_kernel<D, 8, 32, 16><<<dim3(n_rows, nh, (D + 63) / 64), 128, 0, stream>>>(
-      part_o, part_ml, rows, positions, (__nv_bfloat16*)out, nh, window, max_splits);
+      part_o, part_ml, rows, positions, (__nv_bfloat16*)out, nh, window, max_splits,
+      (long long)nh * D, 1.f);
   else
     decode_attention_merge_kernel<D, 4, 8, 8><<<dim3(n_rows, nh, (D + 127) / 128), 128, 0, stream>>>(
-      part_o, part_ml, rows, positions, (__nv_bfloat16*)out, nh, window, max_splits);
+      part_o, part_ml, rows, positions, (__nv_bfloat16*)out, nh, window, max_splits,
+      (long long)nh * D, 1.f);
   return bf_launch_status();
 }
 
@@ -414,22 +416,28 @@ BF_EXPORT int bf_decode_attention(const void* q, const void* k_cache, const void
 
 BF_EXPORT int bf_decode_attention_split_keys() { return DEC_SPLIT; }
 
-// Only the second half: merge the partials that a split kernel left in scratch.
-BF_EXPORT int bf_decode_attention_merge(const float* part_o, const float* part_ml, const int* rows,
-                                        const int* positions, void* out, int n_rows, int nh, int d,
-                                        int window, int max_splits, cudaStream_t stream) {
+// Only the second half: merge the partials that a split kernel left in scratch.  A row of the
+// result starts `out_stride` elements after the row before (a column block of a wider buffer:
+// a multiple of 4, the block 8-byte aligned) and is multiplied by `out_scale`.
+BF_EXPORT int bf_decode_attention_merge_into(const float* part_o, const float* part_ml,
+                                             const int* rows, const int* positions, void* out,
+                                             int n_rows, int nh, int d, int window,
+                                             int max_splits, long long out_stride,
+                                             float out_scale, cudaStream_t stream) {
   if (n_rows <= 0) return 0;
+  if (out_stride < (long long)nh * d || (out_stride & 3) || ((uintptr_t)out & 7))
+    return (int)cudaErrorInvalidValue;
 #define BF_MERGE_CASE(DD)                                                                     \
   case DD:                                                                                    \
     return n_rows * nh <= MERGE_FEW_PAIRS && max_splits >= MERGE_MANY_SPLITS                  \
                ? bf_launch_pdl(decode_attention_merge_kernel<DD, 8, 32, 16>,                  \
                                dim3(n_rows, nh, (DD + 63) / 64), dim3(128), 0, stream, part_o, \
                                part_ml, rows, positions, (__nv_bfloat16*)out, nh, window,     \
-                               max_splits)                                                    \
+                               max_splits, out_stride, out_scale)                             \
                : bf_launch_pdl(decode_attention_merge_kernel<DD, 4, 8, 8>,                    \
                                dim3(n_rows, nh, (DD + 127) / 128), dim3(128), 0, stream,      \
                                part_o, part_ml, rows, positions, (__nv_bfloat16*)out, nh,     \
-                               window, max_splits)
+                               window, max_splits, out_stride, out_scale)
   switch (d) {
     BF_MERGE_CASE(32);
     BF_MERGE_CASE(64);
@@ -440,6 +448,13 @@ BF_EXPORT int bf_decode_attention_merge(const float* part_o, const float* part_m
       return (int)cudaErrorInvalidValue;
   }
 #undef BF_MERGE_CASE
+}
+
+BF_EXPORT int bf_decode_attention_merge(const float* part_o, const float* part_ml, const int* rows,
+                                        const int* positions, void* out, int n_rows, int nh, int d,
+                                        int window, int max_splits, cudaStream_t stream) {
+  return bf_decode_attention_merge_into(part_o, part_ml, rows, positions, out, n_rows, nh, d,
+                                        window, max_splits, (long long)nh * d, 1.f, stream);
 }
 
 // ------------------------------------------------------------------------------

@@ -41,10 +41,11 @@
 #define DP_MAX_SLOTS 8
 #define DP_P_LD 136                        // bf16 elements per row of the probability tile
 
-extern "C" int bf_decode_attention_merge(const float* part_o, const float* part_ml,
-                                         const int* rows, const int* positions, void* out,
-                                         int n_rows, int nh, int d, int window, int max_splits,
-                                         cudaStream_t stream);
+extern "C" int bf_decode_attention_merge_into(const float* part_o, const float* part_ml,
+                                              const int* rows, const int* positions, void* out,
+                                              int n_rows, int nh, int d, int window,
+                                              int max_splits, long long out_stride,
+                                              float out_scale, cudaStream_t stream);
 
 __device__ __forceinline__ int dp_sw_off(int r, int c) { return r * 64 + ((c ^ (r & 7)) << 3); }
 
@@ -154,7 +155,8 @@ decode_attention_persistent_kernel(const __grid_constant__ CUtensorMap map_k,
                                    float* __restrict__ part_o, float* __restrict__ part_ml,
                                    int n_rows, int nh, int nkv, int page_size, int num_pages,
                                    int window, int max_splits, float scale_log2, int slots,
-                                   int groups, int early, int* __restrict__ err) {
+                                   int groups, int early, int* __restrict__ err, float cap_pre,
+                                   float cap_post) {
   constexpr int HALVES = D / 64;
   constexpr int HALF_ELEMS = DP_SPLIT * 64;
   constexpr int TILE_ELEMS = DP_SPLIT * D;
@@ -416,6 +418,17 @@ decode_attention_persistent_kernel(const __grid_constant__ CUtensorMap map_k,
     __syncwarp();
     if (lane == 0) dp_mbar_arrive(empty + slotK);        // K tile, queries and info are in registers
 
+    if (cap_pre > 0.f) {       // s <- (c / scale) tanh(s scale / c): the scale still rides below
+#pragma unroll
+      for (int nt = 0; nt < 4; ++nt) {
+#pragma unroll
+        for (int i = 0; i < 4; ++i) {
+          float t;
+          asm("ex2.approx.ftz.f32 %0, %1;" : "=f"(t) : "f"(s[nt][i] * cap_pre));
+          s[nt][i] = cap_post - __fdividef(2.f * cap_post, t + 1.f);
+        }
+      }
+    }
     float m0 = -INFINITY, m1 = -INFINITY;
 #pragma unroll
     for (int nt = 0; nt < 4; ++nt) {
@@ -538,7 +551,7 @@ static int launch_persistent(const void* q, const void* k_cache, const void* v_c
                              const int* block_tables, int table_stride, float* part_o,
                              float* part_ml, int n_rows, int nh, int nkv, int page_size,
                              int num_pages, int window, int max_splits, float scale, int* err,
-                             cudaStream_t stream) {
+                             cudaStream_t stream, float softcap) {
   const int G = nh / nkv;
   const size_t limit = 227 * 1024;
   int slots = DP_MAX_SLOTS;
@@ -581,30 +594,34 @@ static int launch_persistent(const void* q, const void* k_cache, const void* v_c
                        table_stride, part_o, part_ml, n_rows, nh, nkv, page_size, num_pages,
                        window, max_splits, scale * 1.4426950408889634f, slots, groups,
                        getenv("BINFER_B200_ATTN_EARLY") ? atoi(getenv("BINFER_B200_ATTN_EARLY")) : 1,
-                       err);
+                       err, softcap > 0.f ? 2.f * 1.4426950408889634f * scale / softcap : 0.f,
+                       softcap > 0.f ? softcap / scale : 0.f);
 }
 
-// Same arguments and result as bf_decode_attention.  Returns cudaErrorInvalidValue for what
-// it does not take (see the head of this file); nothing has been launched then.
-BF_EXPORT int bf_decode_attention_persistent(const void* q, const void* k_cache,
-                                             const void* v_cache, const int* rows,
-                                             const int* seq_of_token, const int* positions,
-                                             const int* block_tables, int table_stride, void* out,
-                                             float* part_o, float* part_ml, int n_rows, int nh,
-                                             int nkv, int d, int page_size, int num_pages,
-                                             int window, int max_splits, float scale, int* err,
-                                             cudaStream_t stream) {
+// The arguments and result of bf_decode_attention, and: a soft cap c > 0 on the scaled
+// scores, s <- c tanh(s / c) (0: none); the result's rows `out_stride` elements apart (a
+// column block of a wider buffer) and multiplied by `out_scale`.  Returns
+// cudaErrorInvalidValue for what it does not take (see the head of this file); nothing has
+// been launched then.
+BF_EXPORT int bf_decode_attention_persistent_capped(
+    const void* q, const void* k_cache, const void* v_cache, const int* rows,
+    const int* seq_of_token, const int* positions, const int* block_tables, int table_stride,
+    void* out, float* part_o, float* part_ml, int n_rows, int nh, int nkv, int d, int page_size,
+    int num_pages, int window, int max_splits, float scale, int* err, float softcap,
+    long long out_stride, float out_scale, cudaStream_t stream) {
   if (n_rows <= 0) return 0;
   if (nkv <= 0 || nh % nkv || nh / nkv > 16 || n_rows > DP_MAX_ROWS || page_size < 8 ||
       page_size > 128 || DP_SPLIT % page_size || ((uintptr_t)k_cache & 15) ||
-      ((uintptr_t)v_cache & 15) || ((uintptr_t)q & 15))
+      ((uintptr_t)v_cache & 15) || ((uintptr_t)q & 15) || !(scale > 0.f) || softcap < 0.f ||
+      out_stride < (long long)nh * d || (out_stride & 3) || ((uintptr_t)out & 7))
     return (int)cudaErrorInvalidValue;
   int e;
 #define DP_CASE(DD)                                                                          \
   case DD:                                                                                   \
     e = launch_persistent<DD>(q, k_cache, v_cache, rows, seq_of_token, positions,            \
                               block_tables, table_stride, part_o, part_ml, n_rows, nh, nkv,  \
-                              page_size, num_pages, window, max_splits, scale, err, stream); \
+                              page_size, num_pages, window, max_splits, scale, err, stream,  \
+                              softcap);                                                      \
     break
   switch (d) {
     DP_CASE(64);
@@ -615,8 +632,23 @@ BF_EXPORT int bf_decode_attention_persistent(const void* q, const void* k_cache,
   }
 #undef DP_CASE
   if (e) return e;
-  return bf_decode_attention_merge(part_o, part_ml, rows, positions, out, n_rows, nh, d, window,
-                                   max_splits, stream);
+  return bf_decode_attention_merge_into(part_o, part_ml, rows, positions, out, n_rows, nh, d,
+                                        window, max_splits, out_stride, out_scale, stream);
+}
+
+// Same arguments and result as bf_decode_attention.
+BF_EXPORT int bf_decode_attention_persistent(const void* q, const void* k_cache,
+                                             const void* v_cache, const int* rows,
+                                             const int* seq_of_token, const int* positions,
+                                             const int* block_tables, int table_stride, void* out,
+                                             float* part_o, float* part_ml, int n_rows, int nh,
+                                             int nkv, int d, int page_size, int num_pages,
+                                             int window, int max_splits, float scale, int* err,
+                                             cudaStream_t stream) {
+  return bf_decode_attention_persistent_capped(
+      q, k_cache, v_cache, rows, seq_of_token, positions, block_tables, table_stride, out,
+      part_o, part_ml, n_rows, nh, nkv, d, page_size, num_pages, window, max_splits, scale, err,
+      0.f, (long long)nh * d, 1.f, stream);
 }
 
 BF_TRACE_READER(bf_trace_read_attention_decode_persistent)

@@ -279,8 +279,13 @@ def decode_attention(q: torch.Tensor, k_cache: torch.Tensor, v_cache: torch.Tens
                      positions: torch.Tensor, block_tables: torch.Tensor, out: torch.Tensor,
                      nh: int, nkv: int, d: int, window: Optional[int], scale: float,
                      max_ctx_len: int, err: torch.Tensor, variant: str = "auto",
-                     scratch=None) -> None:
+                     scratch=None, softcap: float = 0.0, out_scale: float = 1.0) -> None:
     """Split-KV attention for rows that bring one token each (bfloat16 only).
+
+    ``softcap`` c > 0: the scaled scores pass ``c tanh(s / c)``; ``out_scale``: a factor on
+    the result; ``out`` may then also be a column block of a wider buffer.  These three are
+    the persistent variant's alone (``decode_attention_takes_capped`` says whether it
+    applies).
 
     ``rows`` lists the token rows to run (None: rows 0..n_rows-1); ``max_ctx_len``
     bounds the context of every such row (a row beyond it sets the error word's
@@ -306,7 +311,16 @@ def decode_attention(q: torch.Tensor, k_cache: torch.Tensor, v_cache: torch.Tens
     if variant == "persistent" and not persistent_ok:
         raise KernelError(f"decode_attention: the persistent variant does not take head_dim {d}, "
                           f"pages of {page_size}, {nh // nkv} heads per kv head, {n_rows} rows")
-    if persistent_ok and variant in ("auto", "persistent"):
+    capped = softcap > 0 or out_scale != 1.0 or not out.is_contiguous()
+    if capped:
+        if not persistent_ok or variant not in ("auto", "persistent"):
+            raise KernelError("decode_attention: a soft cap, an output factor or an output in a "
+                              "column block are the persistent variant's alone")
+        if out.stride(1) != 1 or out.stride(0) % 4 or out.data_ptr() % 8 or out.dtype != q.dtype:
+            raise KernelError("decode_attention: out must have contiguous rows a multiple of 4 "
+                              "elements apart, 8-byte aligned")
+        name, fn = "decode_attention_persistent", lib().bf_decode_attention_persistent_capped
+    elif persistent_ok and variant in ("auto", "persistent"):
         name, fn = "decode_attention_persistent", lib().bf_decode_attention_persistent
     elif tma_ok and variant != "cp_async":
         name, fn = "decode_attention_tma", lib().bf_decode_attention_tma
@@ -329,9 +343,21 @@ def decode_attention(q: torch.Tensor, k_cache: torch.Tensor, v_cache: torch.Tens
          _ptr(block_tables), _c_int(block_tables.stride(0)), _ptr(out), _ptr(part_o),
          _ptr(part_ml), _c_int(n_rows), _c_int(nh), _c_int(nkv), _c_int(d),
          _c_int(page_size), _c_int(k_cache.shape[0]), _c_int(window or 0),
-         _c_int(max_splits), _c_float(scale), _ptr(err), _stream())
+         _c_int(max_splits), _c_float(scale), _ptr(err),
+         *((_c_float(softcap), _c_ll(out.stride(0)), _c_float(out_scale)) if capped else ()),
+         _stream())
     global _launches
     _launches += 1          # two kernels: the splits and their merge
+
+
+def decode_attention_takes_capped(q: torch.Tensor, k_cache: torch.Tensor, nh: int, nkv: int,
+                                  d: int, dv: int, n_rows: int) -> bool:
+    """Whether ``decode_attention`` with a soft cap, an output factor or a strided output
+    (the persistent variant) takes these sizes."""
+    page_size = k_cache.shape[2]
+    return (q.dtype == torch.bfloat16 and d == dv and d in (64, 128, 256)
+            and 8 <= page_size <= 128 and 128 % page_size == 0 and nh // nkv <= 16
+            and n_rows <= 512 and q.is_contiguous() and q.data_ptr() % 16 == 0)
 
 
 # scratch for the shares of split prefill attention, per device (grown as needed, up to a limit)

@@ -33,6 +33,8 @@ from .linear import linear
 # BINFER_B200_CWA_TENSOR_CORES=0: the one-warp-per-row kernel also in bfloat16 (the float32
 # engine always runs it: its sums have one fixed order per position)
 TENSOR_CORES = os.environ.get("BINFER_B200_CWA_TENSOR_CORES", "1") != "0"
+# BINFER_B200_CWA_DECODE_KERNEL=0: steps of single tokens on the tiled kernel too
+DECODE_KERNEL = os.environ.get("BINFER_B200_CWA_DECODE_KERNEL", "1") != "0"
 
 
 class ConvWindowAttention(Mixer):
@@ -145,6 +147,18 @@ class ConvWindowAttention(Mixer):
         if self.taps > 1:
             ops.conv_state_shift(proj, state, ctx.state_slots, ctx.q_start, ctx.B, self.taps)
         keep = s.keep_first if s.window is not None else 0
+        if (DECODE_KERNEL and ctx.decode_only and s.window is None and self.sinks is None
+                and s.softmax_scale > 0 and out.stride(0) % 4 == 0 and out.data_ptr() % 8 == 0
+                and ops.decode_attention_takes_capped(q, view.k_cache, self.H, self.G, self.dk,
+                                                      self.dv, T)):
+            # bfloat16 steps of single tokens, no window and no sinks: the engine's decode
+            # kernel (resident CTAs, tiles by TMA), which takes the soft cap and writes the
+            # scaled result into the branch's columns
+            ops.decode_attention(q, view.k_cache, view.v_cache, None, T, ctx.seq_of_token,
+                                 ctx.positions, ctx.block_tables[g], out, self.H, self.G,
+                                 self.dk, None, s.softmax_scale, ctx.max_ctx_len, ctx.err,
+                                 variant="persistent", softcap=s.softcap, out_scale=out_scale)
+            return
         if (TENSOR_CORES and s.softmax_scale > 0
                 and ops.pwm_attention_takes(proj.dtype, self.H, self.G, self.dk, self.dv)):
             # bfloat16: tiles of (token, head of a group) rows on the tensor cores, prompt

@@ -546,7 +546,7 @@ KET_C = {"architecture": "Ketopel", "vocab": 131, "width": 50, "norm": {"eps": 1
 KET_D = {"architecture": "Ketopel", "vocab": 500, "width": 192, "norm": {"eps": 1e-5},
          "embedding": {"scale": 4.0}, "loop": {"start": 2, "stop": 4, "times": 2},
          "layers": [_ket_layer("latent_attention", _ket_latent(4, 64, 32, 64, 192), ff=512),
-                    _ket_parallel(_ket_left(8, 4, 64, 32, 32, scale=0.11, softcap=50.0,
+                    _ket_parallel(_ket_left(8, 4, 64, 64, 32, scale=0.11, softcap=50.0,
                                             scaling=(4.0, 256, 16.0, 1.0)),
                                   _ket_right(4, 64, 32, (0.97, 0.99, 0.995, 0.999)), ls=0.8,
                                   rs=0.9, ff=320),

@@ -291,6 +291,56 @@ def test_decode_attention_split_kv(cuda_device, nh, nkv, d, ps, window, spike, v
     assert float(out2[0].abs().max()) == 0.0
 
 
+@pytest.mark.parametrize("nh,nkv,d,ps,cap", [(8, 2, 128, 16, 3.0), (6, 3, 64, 8, 0.7),
+                                              (4, 4, 256, 32, 5.0), (16, 8, 128, 64, 0.0)])
+def test_decode_attention_soft_cap_into_a_column_block(cuda_device, nh, nkv, d, ps, cap):
+    """The persistent variant with scores through ``c tanh(s / c)``, the result times a factor
+    and written into a column block of a wider buffer whose other columns stay as they were.
+    The scores are large (a scale of one on long vectors), so a cap left out would show."""
+    from binfer_b200.csrc import ops
+    dev, gen = cuda_device, torch.Generator().manual_seed(nh * 100 + d)
+    ctxs, scale, factor, left, right = [1, 127, 129, 300, 700, 45], 0.5, 1.3, 8, 24
+    kcs, vcs, tables, qs, refs, base = [], [], [], [], [], 0
+    for b, n in enumerate(ctxs):
+        k = torch.randn(n, nkv, d, generator=gen).to(BF16).double()
+        v = torch.randn(n, nkv, d, generator=gen).to(BF16).double()
+        q = torch.randn(nh, d, generator=gen).to(BF16).double()
+        kh = k.repeat_interleave(nh // nkv, dim=1)
+        vh = v.repeat_interleave(nh // nkv, dim=1)
+        sc = torch.einsum("hd,nhd->hn", q, kh) * scale
+        if cap > 0:
+            sc = cap * torch.tanh(sc / cap)
+        refs.append(factor * torch.einsum("hn,nhd->hd", torch.softmax(sc, dim=-1), vh))
+        kc, vc, ids = _paged(k, v, ps, "cpu", BF16, 50 + b, False)
+        kcs.append(kc)
+        vcs.append(vc)
+        tables.append([i + base for i in ids])
+        base += kc.shape[0]
+        qs.append(q)
+    bt = torch.zeros(len(ctxs), max(len(t) for t in tables), dtype=torch.int32)
+    for b, t in enumerate(tables):
+        bt[b, :len(t)] = torch.tensor(t, dtype=torch.int32)
+    q_all = torch.stack(qs).to(BF16).reshape(len(ctxs), nh * d).to(dev)
+    pos = torch.tensor([n - 1 for n in ctxs], dtype=torch.int32, device=dev)
+    sot = torch.arange(len(ctxs), dtype=torch.int32, device=dev)
+    wide = torch.full((len(ctxs), left + nh * d + right), 7.0, dtype=BF16, device=dev)
+    out = wide[:, left:left + nh * d]
+    kc, vc = torch.cat(kcs).to(dev), torch.cat(vcs).to(dev)
+    assert ops.decode_attention_takes_capped(q_all, kc, nh, nkv, d, d, len(ctxs))
+    err = _err(dev)
+    ops.decode_attention(q_all, kc, vc, None, len(ctxs), sot, pos, bt.to(dev), out, nh, nkv, d,
+                         None, scale, max(ctxs) + 300, err, variant="persistent", softcap=cap,
+                         out_scale=factor)
+    assert int(err.item()) == 0
+    _close(out, torch.stack(refs).reshape(len(ctxs), nh * d), BF16)
+    assert bool((wide[:, :left] == 7.0).all()) and bool((wide[:, left + nh * d:] == 7.0).all())
+    if cap > 0:
+        plain = torch.empty((len(ctxs), nh * d), dtype=BF16, device=dev)
+        ops.decode_attention(q_all, kc, vc, None, len(ctxs), sot, pos, bt.to(dev), plain, nh, nkv,
+                             d, None, scale, max(ctxs) + 300, err, variant="persistent")
+        assert float((plain.float() * factor - out.float()).abs().max()) > 0.05
+
+
 @pytest.mark.parametrize("nh,nkv,d,ps,window", [
     (8, 2, 128, 16, None), (32, 8, 128, 16, 300), (6, 3, 64, 8, None), (4, 4, 256, 32, None),
     (8, 4, 128, 64, 1000)])

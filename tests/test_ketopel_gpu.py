@@ -478,6 +478,36 @@ def test_replay(cuda_device, plain_logits, which, dtype, regime):
     _compare(got, ref, dtype, f"{which}/{regime}")
 
 
+def test_single_tokens_take_the_decode_kernel(cuda_device, plain_logits):
+    """Steps of single tokens of the whole-norm attention (heads of 64, a soft cap, the
+    branch's columns of the side-by-side buffer) run on the engine's decode kernel; with it
+    switched off the tiled kernel gives the same logits up to rounding."""
+    from binfer_b200.csrc import ops
+    from binfer_b200.parts import attention_conv_window as mod
+    from binfer_b200.profiling import Profiler
+    reqs = _requests("D")
+    model_dir, ref = plain_logits("D", torch.bfloat16, reqs)
+    steps = H.trace_decode_tail(reqs, tail=24)
+    ps = H.KET["D"]["page_size"]
+    outs = []
+    for on in (True, False):
+        mod.DECODE_KERNEL = on
+        try:
+            prof = Profiler()
+            got = H.run_trace(_runner(model_dir, torch.bfloat16, ps, H.peak_pages(steps, ps)), steps)
+            prof.stop()
+            seen = set(prof.collect())
+        finally:
+            ops.set_profiler(None)
+            mod.DECODE_KERNEL = True
+        assert ("decode_attention_persistent" in seen) == on, sorted(seen)
+        assert "pwm_attention" in seen                      # the prompts' portions
+        _compare(got, ref, torch.bfloat16, f"decode kernel {on}")
+        outs.append(got)
+    worst = max(H.rel_err(outs[0][k], outs[1][k]) for k in outs[0])
+    assert worst <= 0.03, f"the two kernels differ by {worst:.3g}"
+
+
 @pytest.mark.parametrize("which", ["A", "B", "C"])
 def test_the_stream_after_every_layer_run(cuda_device, plain_logits, which):
     """The residual stream after each run of a layer, the looped ones each time: what a pass
