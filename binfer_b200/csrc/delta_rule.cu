@@ -21,12 +21,14 @@
 //
 //   o_t = g (S_old^T q_t) + (k_t . q_t) u_t,
 //
-// and the state's update S <- g S + k u^T then waits for u alone.  k_t . q_t, and the
-// token's k, q and v themselves, are fetched and formed one token ahead, under the chain of
-// the token before.  Up to `stage` tokens are staged in shared memory at a time, in two
-// buffers: the next stage's asynchronous copies travel while this one is walked.  Every sum
-// has an order that depends on the sizes alone, so the result does not depend on how the
-// tokens were cut into steps.
+// and the state's update S <- g S + k u^T then waits for u alone.  Up to `stage` tokens are
+// staged in shared memory at a time, in two buffers: the next stage's asynchronous copies (k,
+// q, v and both gates alike) travel while this one is walked.  When a stage has landed the
+// block forms k_t . q_t for all its tokens, a warp a token; the walk then fetches a token's
+// k, q, v, gates and k . q from shared memory one token ahead, under the chain of the token
+// before.  The lanes of a column (KS, a template parameter: the shuffle rounds unroll) are
+// neighbours in a warp.  Every sum has an order that depends on the sizes alone, so the
+// result does not depend on how the tokens were cut into steps.
 #include "common.cuh"
 
 #define DR_THREADS 128
@@ -36,16 +38,21 @@ __device__ __forceinline__ void dr_cp16(float* smem, const float* gmem) {
   asm volatile("cp.async.cg.shared.global [%0], [%1], 16;" ::"r"(sa), "l"(gmem));
 }
 
-template <int R>
+__device__ __forceinline__ void dr_cp4(float* smem, const float* gmem) {
+  const uint32_t sa = (uint32_t)__cvta_generic_to_shared(smem);
+  asm volatile("cp.async.ca.shared.global [%0], [%1], 4;" ::"r"(sa), "l"(gmem));
+}
+
+template <int R, int KS>
 __global__ void __launch_bounds__(DR_THREADS) delta_scan_kernel(
     const float* __restrict__ qkv, const float* __restrict__ gates, float* __restrict__ state,
     long long state_stride, const int* __restrict__ q_start, const int* __restrict__ state_slots,
-    int n_slots, float* __restrict__ o_raw, int H, int G, int dk, int dv, int KS, int stage,
+    int n_slots, float* __restrict__ o_raw, int H, int G, int dk, int dv, int stage,
     int* __restrict__ err) {
   extern __shared__ __align__(16) float sh[];
   constexpr int R4 = R / 4;
-  const int cols = DR_THREADS / KS;
-  const int dkp = KS * R;                   // dk rounded up to what the lanes of a column hold
+  constexpr int cols = DR_THREADS / KS;
+  constexpr int dkp = KS * R;               // dk rounded up to what the lanes of a column hold
   const int b = blockIdx.z, h = blockIdx.y, col0 = blockIdx.x * cols;
   const int g = h / (H / G);
   const int tid = threadIdx.x;
@@ -75,8 +82,9 @@ __global__ void __launch_bounds__(DR_THREADS) delta_scan_kernel(
     }
   }
 
-  // one buffer: [stage][dkp] q, [stage][dkp] k, [stage][cols] v, [stage][2] beta and decay
-  const int buf_elems = stage * (2 * dkp + cols + 2);
+  // one buffer: [stage][dkp] q, [stage][dkp] k, [stage][cols] v, [stage][2] beta and decay,
+  // [stage] k . q
+  const int buf_elems = stage * (2 * dkp + cols + 3);
   const bool rows16 = (dk & 3) == 0 && (C & 3) == 0;
   auto issue = [&](int s0, int buf) {
     const int sn = min(stage, n - s0);
@@ -107,13 +115,15 @@ __global__ void __launch_bounds__(DR_THREADS) delta_scan_kernel(
     }
     for (int idx = tid; idx < sn * cols; idx += DR_THREADS) {
       const int c = idx / cols, j = idx - c * cols;
-      vd[idx] = col0 + j < dv
-                    ? qkv[(size_t)(t0 + s0 + c) * C + 2 * (size_t)G * dk + (size_t)h * dv + col0 + j]
-                    : 0.f;
+      if (col0 + j < dv)
+        dr_cp4(vd + idx,
+               qkv + (size_t)(t0 + s0 + c) * C + 2 * (size_t)G * dk + (size_t)h * dv + col0 + j);
+      else
+        vd[idx] = 0.f;
     }
     for (int idx = tid; idx < sn * 2; idx += DR_THREADS) {
       const int c = idx >> 1, w = idx & 1;
-      gd[idx] = gates[((size_t)(t0 + s0 + c) * 2 + w) * H + h];
+      dr_cp4(gd + idx, gates + ((size_t)(t0 + s0 + c) * 2 + w) * H + h);
     }
     asm volatile("cp.async.commit_group;" ::);
   };
@@ -132,6 +142,15 @@ __global__ void __launch_bounds__(DR_THREADS) delta_scan_kernel(
     const float* ks = qs + stage * dkp;
     const float* vs = ks + stage * dkp;
     const float* gs = vs + stage * cols;
+    float* kqs = sh + (size_t)buf * buf_elems + stage * (2 * dkp + cols + 2);
+    for (int c = tid >> 5; c < sn; c += DR_THREADS / 32) {   // a warp a token
+      float d = 0.f;
+      for (int i = tid & 31; i < dkp; i += 32) d = fmaf(ks[c * dkp + i], qs[c * dkp + i], d);
+#pragma unroll
+      for (int o = 16; o > 0; o >>= 1) d += __shfl_xor_sync(0xffffffffu, d, o);
+      if ((tid & 31) == 0) kqs[c] = d;
+    }
+    __syncthreads();
     // a token's k, q, v, gates and k . q, held one token ahead in two sets of registers
     float4 kk[2][R4], qq[2][R4];
     float vv[2], be[2], de[2], kq[2];
@@ -139,18 +158,11 @@ __global__ void __launch_bounds__(DR_THREADS) delta_scan_kernel(
   {                                                                                     \
     const float4* kr = reinterpret_cast<const float4*>(ks + (size_t)(c) * dkp) + part;  \
     const float4* qr = reinterpret_cast<const float4*>(qs + (size_t)(c) * dkp) + part;  \
-    float d0 = 0.f, d1 = 0.f;                                                           \
     _Pragma("unroll") for (int r4 = 0; r4 < R4; ++r4) {                                 \
       kk[bi][r4] = kr[r4 * KS];                                                         \
       qq[bi][r4] = qr[r4 * KS];                                                         \
-      d0 = fmaf(kk[bi][r4].x, qq[bi][r4].x, d0);                                        \
-      d1 = fmaf(kk[bi][r4].y, qq[bi][r4].y, d1);                                        \
-      d0 = fmaf(kk[bi][r4].z, qq[bi][r4].z, d0);                                        \
-      d1 = fmaf(kk[bi][r4].w, qq[bi][r4].w, d1);                                        \
     }                                                                                   \
-    float d = d0 + d1;                                                                  \
-    for (int o = 1; o < KS; o <<= 1) d += __shfl_xor_sync(0xffffffffu, d, o);           \
-    kq[bi] = d;                                                                         \
+    kq[bi] = kqs[(c)];                                                                  \
     vv[bi] = vs[(c) * cols + cg];                                                       \
     be[bi] = gs[2 * (c)];                                                               \
     de[bi] = gs[2 * (c) + 1];                                                           \
@@ -171,7 +183,7 @@ __global__ void __launch_bounds__(DR_THREADS) delta_scan_kernel(
     float sk = (a0 + a1) + (a2 + a3), sq = (b0 + b1) + (b2 + b3);                       \
     const float decay = de[bi];                                                         \
     _Pragma("unroll") for (int r = 0; r < R; ++r) S[r] *= decay;                        \
-    for (int o = 1; o < KS; o <<= 1) {                                                  \
+    _Pragma("unroll") for (int o = 1; o < KS; o <<= 1) {                                \
       sk += __shfl_xor_sync(0xffffffffu, sk, o);                                        \
       sq += __shfl_xor_sync(0xffffffffu, sq, o);                                        \
     }                                                                                   \
@@ -220,25 +232,30 @@ BF_EXPORT int bf_delta_scan(const float* qkv, const float* gates, float* state,
   if (B <= 0 || T <= 0) return 0;
   if (dk <= 0 || dv <= 0 || dk > 1024 || G <= 0 || H % G) return (int)cudaErrorInvalidValue;
   const int R = dk <= 128 ? 16 : 32;
-  int KS = 1;
+  int KS = dk <= 128 ? 1 : 8;
   while (KS * R < dk) KS <<= 1;
   const int cols = DR_THREADS / KS;
-  const size_t per_token = (size_t)(2 * KS * R + cols + 2) * sizeof(float);
+  const size_t per_token = (size_t)(2 * KS * R + cols + 3) * sizeof(float);
   int stage = 32;
   while (stage > 2 && stage / 2 >= max_q) stage >>= 1;
   while (stage > 2 && 2 * stage * per_token > 64 * 1024) stage >>= 1;
   const size_t smem = 2 * stage * per_token;
   dim3 grid((dv + cols - 1) / cols, H, B);
-#define DR_GO(RR)                                                                              \
+#define DR_GO(RR, KK)                                                                          \
   {                                                                                            \
     if (smem > 48 * 1024)                                                                      \
-      cudaFuncSetAttribute(delta_scan_kernel<RR>, cudaFuncAttributeMaxDynamicSharedMemorySize, \
-                           (int)smem);                                                         \
-    delta_scan_kernel<RR><<<grid, DR_THREADS, smem, stream>>>(                                 \
+      cudaFuncSetAttribute(delta_scan_kernel<RR, KK>,                                          \
+                           cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);            \
+    delta_scan_kernel<RR, KK><<<grid, DR_THREADS, smem, stream>>>(                             \
         qkv, gates, state, state_stride, q_start, state_slots, n_slots, o_raw, H, G, dk, dv,   \
-        KS, stage, err);                                                                       \
+        stage, err);                                                                           \
   }
-  if (R == 16) DR_GO(16) else DR_GO(32)
+  if (R == 16) {
+    if (KS == 1) DR_GO(16, 1) else if (KS == 2) DR_GO(16, 2) else if (KS == 4) DR_GO(16, 4)
+    else DR_GO(16, 8)
+  } else {
+    if (KS == 8) DR_GO(32, 8) else if (KS == 16) DR_GO(32, 16) else DR_GO(32, 32)
+  }
 #undef DR_GO
   return bf_launch_status();
 }
