@@ -82,7 +82,8 @@ prefill_attention_umma2_kernel(const __grid_constant__ CUtensorMap map_q,
                                __nv_bfloat16* __restrict__ out, int nh, int nkv, int page_size,
                                int num_pages, int window, float scale_log2, int splits,
                                float* __restrict__ part_o, float* __restrict__ part_ml,
-                               int* __restrict__ err) {
+                               int* __restrict__ err, float cap_pre, float cap_post,
+                               long long out_stride, float out_scale) {
   constexpr int D = A2_D;
   constexpr int HALVES = D / 64;
   constexpr int QHALF_BYTES = A2_BM * 128;               // 128 query rows of 128 bytes
@@ -358,6 +359,13 @@ prefill_attention_umma2_kernel(const __grid_constant__ CUtensorMap map_q,
         tc_fence_after();
         uint32_t v[32];            // v[4c + 2e + i]: row e, key column 8c + 2 q4 + i
         tmem_ld_frag64(my_s + (uint32_t)((n & 1) * A2_BN), v);
+        if (cap_pre > 0.f) {     // s <- (c / scale) tanh(s scale / c): the scale still rides below
+#pragma unroll
+          for (int i = 0; i < 32; ++i) {
+            const float t = ex2_approx(__uint_as_float(v[i]) * cap_pre);
+            v[i] = __float_as_uint(cap_post - __fdividef(2.f * cap_post, t + 1.f));
+          }
+        }
         const int t_lo = (kt_first + n) * A2_BN + 2 * q4;  // key of this thread's first column
         int hi[2], lo[2];          // last and first visible key, counted from t_lo
         bool need_mask[2];
@@ -496,8 +504,8 @@ prefill_attention_umma2_kernel(const __grid_constant__ CUtensorMap map_q,
         }
       } else if (ok) {
         tc_fence_after();
-        const float inv = 1.f / xl[r];
-        __nv_bfloat16* dst = out + ((size_t)(row0 + l) * nh + h) * D + half * OH;
+        const float inv = out_scale / xl[r];
+        __nv_bfloat16* dst = out + (size_t)(row0 + l) * out_stride + (size_t)h * D + half * OH;
 #pragma unroll 1
         for (int c0 = 0; c0 < OH; c0 += 32) {
           uint32_t w[32];
@@ -544,7 +552,8 @@ prefill_attention_umma2_kernel(const __grid_constant__ CUtensorMap map_q,
 __global__ void prefill_attention_merge_kernel(const float* __restrict__ part_o,
                                                const float* __restrict__ part_ml,
                                                const int* __restrict__ items,
-                                               __nv_bfloat16* __restrict__ out, int nh, int splits) {
+                                               __nv_bfloat16* __restrict__ out, int nh, int splits,
+                                               long long out_stride, float out_scale) {
   const int* it = items + 4 * blockIdx.z;
   const int row0 = it[1], qlen = it[2];
   const int r = blockIdx.x * 4 + (threadIdx.x >> 5), h = blockIdx.y, lane = threadIdx.x & 31;
@@ -565,12 +574,13 @@ __global__ void prefill_attention_merge_kernel(const float* __restrict__ part_o,
     acc.z += o.z * w;
     acc.w += o.w * w;
   }
-  const float inv = L > 0.f ? 1.f / L : 0.f;
+  const float inv = L > 0.f ? out_scale / L : 0.f;
   uint2 packed;
   __nv_bfloat162* o2 = reinterpret_cast<__nv_bfloat162*>(&packed);
   o2[0] = __floats2bfloat162_rn(acc.x * inv, acc.y * inv);
   o2[1] = __floats2bfloat162_rn(acc.z * inv, acc.w * inv);
-  *reinterpret_cast<uint2*>(out + ((size_t)(row0 + r) * nh + h) * A2_D + lane * 4) = packed;
+  *reinterpret_cast<uint2*>(out + (size_t)(row0 + r) * out_stride + (size_t)h * A2_D + lane * 4) =
+      packed;
 }
 
 }  // namespace
@@ -579,20 +589,26 @@ __global__ void prefill_attention_merge_kernel(const float* __restrict__ part_o,
 // queries out over that many CTAs (for few queries after many cached keys); part_o (float
 // [total_rows, nh, splits, 128]) and part_ml (float [total_rows, nh, splits, 2]) take their
 // partial results, which a second kernel merges.  Head size 128 only, pages of 8..64 keys that
-// divide 64; cudaErrorInvalidValue otherwise (nothing launched).
-BF_EXPORT int bf_prefill_attention_umma2(const void* q, const void* k_cache, const void* v_cache,
-                                         const int* items, int n_items, int max_rows,
-                                         int total_rows, const int* block_tables,
-                                         int table_stride, void* out, int nh, int nkv, int d,
-                                         int page_size, int num_pages, int window, float scale,
-                                         int splits, float* part_o, float* part_ml, int* err,
-                                         cudaStream_t stream) {
+// divide 64; cudaErrorInvalidValue otherwise (nothing launched).  And: a soft cap c > 0 on the
+// scaled scores, s <- c tanh(s / c) (0: none); the result's rows `out_stride` elements apart
+// (a column block of a wider buffer: a multiple of 8, the block 16-byte aligned) and
+// multiplied by `out_scale`.
+BF_EXPORT int bf_prefill_attention_umma2_capped(
+    const void* q, const void* k_cache, const void* v_cache, const int* items, int n_items,
+    int max_rows, int total_rows, const int* block_tables, int table_stride, void* out, int nh,
+    int nkv, int d, int page_size, int num_pages, int window, float scale, int splits,
+    float* part_o, float* part_ml, int* err, float softcap, long long out_stride,
+    float out_scale, cudaStream_t stream) {
   if (n_items <= 0 || max_rows <= 0) return 0;
   if (splits < 1 || (splits > 1 && (!part_o || !part_ml))) return (int)cudaErrorInvalidValue;
   if (d != A2_D || nkv <= 0 || nh % nkv || page_size < 8 || page_size > A2_BN ||
       A2_BN % page_size || ((uintptr_t)q & 15) || ((uintptr_t)k_cache & 15) ||
-      ((uintptr_t)v_cache & 15) || ((uintptr_t)out & 15))
+      ((uintptr_t)v_cache & 15) || ((uintptr_t)out & 15) || !(scale > 0.f) || softcap < 0.f ||
+      out_stride < (long long)nh * A2_D || (out_stride & 7))
     return (int)cudaErrorInvalidValue;
+  const float log2e = 1.4426950408889634f;
+  const float cap_pre = softcap > 0.f ? 2.f * log2e * scale / softcap : 0.f;
+  const float cap_post = softcap > 0.f ? softcap / scale : 0.f;
   CUtensorMap mq, mk, mv;
   int e = bf_make_tensor_map_bf16_2d(&mq, q, total_rows, (long long)nh * A2_D,
                                      (long long)nh * A2_D, A2_BM, 64);
@@ -624,12 +640,26 @@ BF_EXPORT int bf_prefill_attention_umma2(const void* q, const void* k_cache, con
   if (grid.y > 65535u || grid.z > 65535u) return (int)cudaErrorInvalidValue;
   kern<<<grid, A2_THREADS, smem, stream>>>(mq, mk, mv, mkr, mvr, items, block_tables, table_stride,
                                            (__nv_bfloat16*)out, nh, nkv, page_size, num_pages,
-                                           window, scale * 1.4426950408889634f, splits, part_o, part_ml, err);
+                                           window, scale * log2e, splits, part_o, part_ml, err,
+                                           cap_pre, cap_post, out_stride, out_scale);
   if (splits > 1) {
     int st = bf_launch_status();
     if (st) return st;
     prefill_attention_merge_kernel<<<dim3((max_rows + 3) / 4, nh, n_items), 128, 0, stream>>>(
-        part_o, part_ml, items, (__nv_bfloat16*)out, nh, splits);
+        part_o, part_ml, items, (__nv_bfloat16*)out, nh, splits, out_stride, out_scale);
   }
   return bf_launch_status();
+}
+
+BF_EXPORT int bf_prefill_attention_umma2(const void* q, const void* k_cache, const void* v_cache,
+                                         const int* items, int n_items, int max_rows,
+                                         int total_rows, const int* block_tables,
+                                         int table_stride, void* out, int nh, int nkv, int d,
+                                         int page_size, int num_pages, int window, float scale,
+                                         int splits, float* part_o, float* part_ml, int* err,
+                                         cudaStream_t stream) {
+  return bf_prefill_attention_umma2_capped(q, k_cache, v_cache, items, n_items, max_rows,
+                                           total_rows, block_tables, table_stride, out, nh, nkv,
+                                           d, page_size, num_pages, window, scale, splits, part_o,
+                                           part_ml, err, 0.f, (long long)nh * A2_D, 1.f, stream);
 }

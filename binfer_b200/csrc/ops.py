@@ -369,7 +369,8 @@ def prefill_attention(q: torch.Tensor, k_cache: torch.Tensor, v_cache: torch.Ten
                       items: torch.Tensor, n_items: int, max_rows: int,
                       block_tables: torch.Tensor, out: torch.Tensor, nh: int, nkv: int, d: int,
                       window: Optional[int], scale: float, err: torch.Tensor,
-                      variant: str = "auto", max_ctx: int = 0, splits: int = 0) -> None:
+                      variant: str = "auto", max_ctx: int = 0, splits: int = 0,
+                      softcap: float = 0.0, out_scale: float = 1.0) -> None:
     """Causal flash attention over the pages for prompt portions (bfloat16 only).
     ``items`` int32 [n, 4]: (request index, first token row, rows, first position).
     ``variant``: ``umma2`` (tcgen05 tensor cores, one CTA per SM with two query tiles sharing a
@@ -379,7 +380,11 @@ def prefill_attention(q: torch.Tensor, k_cache: torch.Tensor, v_cache: torch.Ten
     blocks of 256 rows for most SMs, else umma where it applies, else mma_sync.
     ``max_ctx``: the longest context among the portions, if the caller knows it: few query
     rows after many cached keys then have their keys shared out over several CTAs of the umma2
-    kernel, whose partial results a second kernel merges (``splits`` forces a number)."""
+    kernel, whose partial results a second kernel merges (``splits`` forces a number).
+
+    ``softcap`` c > 0: the scaled scores pass ``c tanh(s / c)``; ``out_scale``: a factor on
+    the result; ``out`` may then also be a column block of a wider buffer.  These three are
+    the umma2 variant's alone (``prefill_attention_takes_capped``)."""
     global _launches
     if q.dtype != torch.bfloat16 or d not in DECODE_HEAD_DIMS:
         raise KernelError(f"prefill_attention: bfloat16 and head_dim in {DECODE_HEAD_DIMS} only")
@@ -399,6 +404,18 @@ def prefill_attention(q: torch.Tensor, k_cache: torch.Tensor, v_cache: torch.Ten
     blocks2 = -(-max_rows // 256) * nh * n_items
     use2 = umma2_ok and (variant == "umma2" or (variant == "auto" and (
         blocks2 >= 120 or max_rows > 256 or max_ctx >= 2048)))
+    capped = softcap > 0 or out_scale != 1.0 or not out.is_contiguous()
+    fn2, tail2 = lib().bf_prefill_attention_umma2, ()
+    if capped:
+        if not umma2_ok or variant not in ("auto", "umma2"):
+            raise KernelError("prefill_attention: a soft cap, an output factor or an output in a "
+                              "column block are the umma2 variant's alone")
+        if out.stride(1) != 1 or out.stride(0) % 8 or out.data_ptr() % 16 or out.dtype != q.dtype:
+            raise KernelError("prefill_attention: out must have contiguous rows a multiple of 8 "
+                              "elements apart, 16-byte aligned")
+        use2 = True
+        fn2 = lib().bf_prefill_attention_umma2_capped
+        tail2 = (_c_float(softcap), _c_ll(out.stride(0)), _c_float(out_scale))
     # Few blocks and long contexts: share the keys of each block out (at least 16 key tiles a
     # share, at most 8 shares, no more CTAs than SMs).
     if splits <= 0:
@@ -415,22 +432,22 @@ def prefill_attention(q: torch.Tensor, k_cache: torch.Tensor, v_cache: torch.Ten
                 buf = _prefill_split_scratch[key] = (
                     torch.empty(need * d, dtype=torch.float32, device=q.device),
                     torch.empty(need * 2, dtype=torch.float32, device=q.device))
-            _run("prefill_attention_umma2", lib().bf_prefill_attention_umma2,
+            _run("prefill_attention_umma2", fn2,
                  _ptr(q), _ptr(k_cache), _ptr(v_cache), _ptr(items), _c_int(n_items),
                  _c_int(max_rows), _c_int(T), _ptr(block_tables),
                  _c_int(block_tables.stride(0)), _ptr(out), _c_int(nh), _c_int(nkv), _c_int(d),
                  _c_int(page_size), _c_int(k_cache.shape[0]), _c_int(window or 0),
                  _c_float(scale), _c_int(splits), _ptr(buf[0]), _ptr(buf[1]), _ptr(err),
-                 _stream())
+                 *tail2, _stream())
             _launches += 1          # two kernels: the shares and their merge
             return
     if use2:
-        _run("prefill_attention_umma2", lib().bf_prefill_attention_umma2,
+        _run("prefill_attention_umma2", fn2,
              _ptr(q), _ptr(k_cache), _ptr(v_cache), _ptr(items), _c_int(n_items),
              _c_int(max_rows), _c_int(q.shape[0]), _ptr(block_tables),
              _c_int(block_tables.stride(0)), _ptr(out), _c_int(nh), _c_int(nkv), _c_int(d),
              _c_int(page_size), _c_int(k_cache.shape[0]), _c_int(window or 0), _c_float(scale),
-             _c_int(1), None, None, _ptr(err), _stream())
+             _c_int(1), None, None, _ptr(err), *tail2, _stream())
         return
     if umma_ok and variant != "mma_sync":
         name = "prefill_attention_umma"
@@ -446,6 +463,15 @@ def prefill_attention(q: torch.Tensor, k_cache: torch.Tensor, v_cache: torch.Ten
          _ptr(block_tables), _c_int(block_tables.stride(0)), _ptr(out), _c_int(nh), _c_int(nkv),
          _c_int(d), _c_int(page_size), _c_int(k_cache.shape[0]), _c_int(window or 0),
          _c_float(scale), _ptr(err), _stream())
+
+
+def prefill_attention_takes_capped(q: torch.Tensor, k_cache: torch.Tensor, d: int,
+                                   dv: int) -> bool:
+    """Whether ``prefill_attention`` with a soft cap, an output factor or a strided output (the
+    umma2 variant) takes these sizes."""
+    page_size = k_cache.shape[2]
+    return (q.dtype == torch.bfloat16 and d == dv == 128 and 8 <= page_size <= 64
+            and 64 % page_size == 0 and q.is_contiguous() and q.data_ptr() % 16 == 0)
 
 
 # ------------------------------------------------------------------ layer norm

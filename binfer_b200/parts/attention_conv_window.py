@@ -33,8 +33,12 @@ from .linear import linear
 # BINFER_B200_CWA_TENSOR_CORES=0: the one-warp-per-row kernel also in bfloat16 (the float32
 # engine always runs it: its sums have one fixed order per position)
 TENSOR_CORES = os.environ.get("BINFER_B200_CWA_TENSOR_CORES", "1") != "0"
-# BINFER_B200_CWA_DECODE_KERNEL=0: steps of single tokens on the tiled kernel too
+# BINFER_B200_CWA_DECODE_KERNEL=0: steps of single tokens, and steps of long prompt portions
+# alone, on the tiled kernel too
 DECODE_KERNEL = os.environ.get("BINFER_B200_CWA_DECODE_KERNEL", "1") != "0"
+# the longest portion of a step from which the engine's prefill kernel (blocks of 256 rows a
+# head) is taken instead of the tiled kernel
+PREFILL_KERNEL_ROWS = 256
 
 
 class ConvWindowAttention(Mixer):
@@ -158,6 +162,19 @@ class ConvWindowAttention(Mixer):
                                  ctx.positions, ctx.block_tables[g], out, self.H, self.G,
                                  self.dk, None, s.softmax_scale, ctx.max_ctx_len, ctx.err,
                                  variant="persistent", softcap=s.softcap, out_scale=out_scale)
+            return
+        if (DECODE_KERNEL and not ctx.decode_only and ctx.n_decode == 0 and ctx.n_prefill
+                and ctx.max_prefill_rows >= PREFILL_KERNEL_ROWS and s.window is None
+                and self.sinks is None and s.softmax_scale > 0 and out.stride(0) % 8 == 0
+                and out.data_ptr() % 16 == 0
+                and ops.prefill_attention_takes_capped(q, view.k_cache, self.dk, self.dv)):
+            # bfloat16 steps of prompt portions alone, heads of 128: the engine's tcgen05
+            # prefill kernel, which takes the soft cap and writes into the branch's columns
+            ops.prefill_attention(q, view.k_cache, view.v_cache, ctx.prefill_items,
+                                  ctx.n_prefill, ctx.max_prefill_rows, ctx.block_tables[g], out,
+                                  self.H, self.G, self.dk, None, s.softmax_scale, ctx.err,
+                                  variant="umma2", max_ctx=ctx.max_ctx_len, softcap=s.softcap,
+                                  out_scale=out_scale)
             return
         if (TENSOR_CORES and s.softmax_scale > 0
                 and ops.pwm_attention_takes(proj.dtype, self.H, self.G, self.dk, self.dv)):

@@ -825,6 +825,60 @@ def test_prefill_attention_over_pages(cuda_device, nh, nkv, d, ps, window, spike
     assert torch.equal(out2[70:112], out[70:112]) and float(out2[:70].abs().max()) == 0.0
 
 
+@pytest.mark.parametrize("nh,nkv,ps,cap,splits", [(4, 2, 16, 3.0, 1), (6, 6, 8, 0.7, 3),
+                                                   (2, 1, 64, 0.0, 1), (8, 2, 16, 5.0, 2)])
+def test_prefill_attention_soft_cap_into_a_column_block(cuda_device, nh, nkv, ps, cap, splits):
+    """The umma2 variant with scores through ``c tanh(s / c)``, the result times a factor and
+    written into a column block of a wider buffer whose other columns stay as they were, with
+    and without the keys shared out.  The scores are large, so a cap left out would show."""
+    from binfer_b200.csrc import ops
+    dev, d, gen = cuda_device, 128, torch.Generator().manual_seed(nh * 10 + ps)
+    ctxs, qlens = [300, 70, 1100, 2, 257], [300, 37, 260, 2, 129]
+    scale, factor, left, right = 0.5, 0.8, 16, 8
+    kcs, vcs, tables, qs, refs, items, base, row = [], [], [], [], [], [], 0, 0
+    for b, (n, ql) in enumerate(zip(ctxs, qlens)):
+        k = torch.randn(n, nkv, d, generator=gen).to(BF16).double()
+        v = torch.randn(n, nkv, d, generator=gen).to(BF16).double()
+        q = torch.randn(ql, nh, d, generator=gen).to(BF16).double()
+        kh = k.repeat_interleave(nh // nkv, dim=1)
+        vh = v.repeat_interleave(nh // nkv, dim=1)
+        sc = torch.einsum("qhd,nhd->hqn", q, kh) * scale
+        if cap > 0:
+            sc = cap * torch.tanh(sc / cap)
+        seen = torch.arange(n)[None, :] <= (n - ql + torch.arange(ql))[:, None]
+        sc = sc.masked_fill(~seen[None], float("-inf"))
+        refs.append(factor * torch.einsum("hqn,nhd->qhd", torch.softmax(sc, dim=-1), vh))
+        kc, vc, ids = _paged(k, v, ps, "cpu", BF16, 70 + b, False)
+        kcs.append(kc)
+        vcs.append(vc)
+        tables.append([i + base for i in ids])
+        base += kc.shape[0]
+        qs.append(q)
+        items.append([b, row, ql, n - ql])
+        row += ql
+    bt = torch.zeros(len(ctxs), max(len(t) for t in tables), dtype=torch.int32)
+    for b, t in enumerate(tables):
+        bt[b, :len(t)] = torch.tensor(t, dtype=torch.int32)
+    q_all = torch.cat(qs).to(BF16).reshape(row, nh * d).to(dev)
+    items = torch.tensor(items, dtype=torch.int32, device=dev)
+    wide = torch.full((row, left + nh * d + right), 7.0, dtype=BF16, device=dev)
+    out = wide[:, left:left + nh * d]
+    kc, vc = torch.cat(kcs).to(dev), torch.cat(vcs).to(dev)
+    assert ops.prefill_attention_takes_capped(q_all, kc, d, d)
+    err = _err(dev)
+    ops.prefill_attention(q_all, kc, vc, items, len(ctxs), max(qlens), bt.to(dev), out, nh, nkv,
+                          d, None, scale, err, variant="umma2", splits=splits, softcap=cap,
+                          out_scale=factor)
+    assert int(err.item()) == 0
+    _close(out, torch.cat(refs).reshape(row, nh * d), BF16)
+    assert bool((wide[:, :left] == 7.0).all()) and bool((wide[:, left + nh * d:] == 7.0).all())
+    if cap > 0:
+        plain = torch.empty((row, nh * d), dtype=BF16, device=dev)
+        ops.prefill_attention(q_all, kc, vc, items, len(ctxs), max(qlens), bt.to(dev), plain, nh,
+                              nkv, d, None, scale, err, variant="umma2", splits=splits)
+        assert float((plain.float() * factor - out.float()).abs().max()) > 0.05
+
+
 @pytest.mark.parametrize("splits", [2, 3, 8])
 @pytest.mark.parametrize("ps,neighbours", [(16, True), (8, False), (64, False)])
 def test_prefill_attention_keys_shared_out(cuda_device, splits, ps, neighbours):

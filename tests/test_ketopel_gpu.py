@@ -508,6 +508,40 @@ def test_single_tokens_take_the_decode_kernel(cuda_device, plain_logits):
     assert worst <= 0.03, f"the two kernels differ by {worst:.3g}"
 
 
+def test_long_portions_take_the_prefill_kernel(cuda_device, tmp_path):
+    """Whole prompts of 300 and 280 tokens through a side-by-side layer whose softmax branch
+    has heads of 128 and a soft cap run on the engine's tcgen05 prefill kernel (writing the
+    scaled result into the branch's columns); with it switched off the tiled kernel gives the
+    same logits up to rounding."""
+    from binfer_b200.csrc import ops
+    from binfer_b200.parts import attention_conv_window as mod
+    from binfer_b200.profiling import Profiler
+    left = H._ket_left(4, 2, 128, 128, 64, scale=0.1, softcap=4.0, scaling=(4.0, 64, 8.0, 1.0))
+    raw = _one_layer(H._ket_parallel(left, H._ket_right(2, 16, 16, (0.9, 0.97)), ls=1.1, rs=0.6,
+                                     ff=96), vocab=300, width=128)
+    d = H.make_ketopel_dir(tmp_path, "A", torch.bfloat16, raw=raw, tag="long")
+    raw, w = H.read_model_dir(d)
+    reqs = {"a": H.random_tokens(300, raw["vocab"], 5), "b": H.random_tokens(280, raw["vocab"], 6)}
+    ref = {rid: P.forward(raw, w, toks) for rid, toks in reqs.items()}
+    steps = H.trace_whole(reqs)
+    outs = []
+    for on in (True, False):
+        mod.DECODE_KERNEL = on
+        try:
+            prof = Profiler()
+            got = H.run_trace(_runner(d, torch.bfloat16, 16, H.peak_pages(steps, 16)), steps)
+            prof.stop()
+            seen = set(prof.collect())
+        finally:
+            ops.set_profiler(None)
+            mod.DECODE_KERNEL = True
+        assert ("prefill_attention_umma2" in seen) == on and ("pwm_attention" in seen) != on, sorted(seen)
+        _compare(got, ref, torch.bfloat16, f"prefill kernel {on}")
+        outs.append(got)
+    worst = max(H.rel_err(outs[0][k], outs[1][k]) for k in outs[0])
+    assert worst <= 0.03, f"the two kernels differ by {worst:.3g}"
+
+
 @pytest.mark.parametrize("which", ["A", "B", "C"])
 def test_the_stream_after_every_layer_run(cuda_device, plain_logits, which):
     """The residual stream after each run of a layer, the looped ones each time: what a pass
