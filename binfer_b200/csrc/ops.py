@@ -602,12 +602,14 @@ def retention_scan(proj: torch.Tensor, q_off: int, k_off: int, v_off: int, decay
     if 2 * rot_half > dk:
         raise KernelError("retention_scan: more rotated sizes than a head has")
     T = proj.shape[0]
-    # the turned q and k of every token in float: written by the first of the two kernels
+    # the turned q and k and the values of every token in float: written by the first of the
+    # two kernels
     qk = torch.empty((T, 2, heads, dk), dtype=torch.float32, device=proj.device)
+    vf = torch.empty((T, heads, dv), dtype=torch.float32, device=proj.device)
     _run("retention_scan", lib().bf_retention_scan, _ptr(proj), _c_ll(proj.stride(0)),
          _c_ll(q_off), _c_ll(k_off), _c_ll(v_off), _ptr(decays), _ptr(inv_freq), _c_int(rot_half),
          _ptr(positions), _ptr(state), _c_ll(state.stride(0)), _ptr(q_start), _ptr(state_slots),
-         _c_int(state.shape[0]), _ptr(o_raw), _ptr(qk), _c_int(T), _c_int(B),
+         _c_int(state.shape[0]), _ptr(o_raw), _ptr(qk), _ptr(vf), _c_int(T), _c_int(B),
          _c_int(max_q if max_q > 0 else T), _c_int(heads), _c_int(dk), _c_int(dv), _c_float(k_scale), _c_int(_dtype_code(proj)), _ptr(err),
          _c_int(1 if silu else 0), _stream())
     global _launches

@@ -11,8 +11,9 @@
 // With `act` 1, q, k and v pass silu first (lightning attention).
 //
 // retention_encode: q and k of every (token, head), turned and scaled, as float rows
-// `qk [T][2][H][dk]` (one warp per (token, head); the scan's blocks, several per head, read
-// them from there instead of each turning them again).
+// `qk [T][2][H][dk]`, and the head's v in float `vf [T][H][dv]` (one warp per (token, head);
+// the scan's blocks, several per head, read them from there by asynchronous copies instead
+// of each turning and converting them again).
 //
 // retention_scan: a block owns `cols` output columns of one (request, head); a column is
 // shared by KS adjacent lanes that each hold R consecutive state elements of it in registers
@@ -40,7 +41,8 @@ __global__ void retention_encode_kernel(const A* __restrict__ proj, long long st
                                         const float* __restrict__ inv_freq, int rot_half,
                                         const int* __restrict__ positions,
                                         float* __restrict__ qk, int T, int H, int dk,
-                                        float k_scale, int act) {
+                                        float k_scale, int act, long long v_off, int dv,
+                                        float* __restrict__ vf) {
   const long long item = ((long long)blockIdx.x * blockDim.x + threadIdx.x) >> 5;
   const int lane = threadIdx.x & 31;
   if (item >= (long long)T * H) return;
@@ -71,6 +73,14 @@ __global__ void retention_encode_kernel(const A* __restrict__ proj, long long st
     qo[i] = qv;
     ko[i] = kv * k_scale;
   }
+  // the head's values in float (activation applied), for the scan's asynchronous copies
+  const A* vrow = proj + (size_t)t * stride + v_off + (size_t)h * dv;
+  float* vo = vf + ((size_t)t * H + h) * dv;
+  for (int i = lane; i < dv; i += 32) {
+    float x = bf_ld(vrow + i);
+    if (act) x = x / (1.f + expf(-x));
+    vo[i] = x;
+  }
 }
 
 __device__ __forceinline__ void ret_cp16(float* smem, const float* gmem) {
@@ -80,14 +90,21 @@ __device__ __forceinline__ void ret_cp16(float* smem, const float* gmem) {
 
 // R: state elements along dk that a lane holds per column; CV: columns a lane holds (its
 // state tile is CV x R: a token's k and q values are then fetched once for CV columns).
-template <typename A, int R, int CV>
+__device__ __forceinline__ void ret_cp4(float* smem, const float* gmem) {
+  const uint32_t sa = (uint32_t)__cvta_generic_to_shared(smem);
+  asm volatile("cp.async.ca.shared.global [%0], [%1], 4;" ::"r"(sa), "l"(gmem));
+}
+
+// KST: the lanes per column where they are known when the kernel is compiled (the rounds of
+// shuffles then unroll), 0: `ks_rt` of them.
+template <int R, int CV, int KST>
 __global__ void __launch_bounds__(RET_THREADS) retention_scan_kernel(
-    const A* __restrict__ proj, long long stride, long long v_off,
-    const float* __restrict__ qk, const float* __restrict__ decays, float* __restrict__ state,
-    long long state_stride, const int* __restrict__ q_start, const int* __restrict__ state_slots,
-    int n_slots, float* __restrict__ o_raw, int H, int dk, int dv, int KS, int stage,
-    int* __restrict__ err, int act) {
+    const float* __restrict__ vf, const float* __restrict__ qk, const float* __restrict__ decays,
+    float* __restrict__ state, long long state_stride, const int* __restrict__ q_start,
+    const int* __restrict__ state_slots, int n_slots, float* __restrict__ o_raw, int H, int dk,
+    int dv, int ks_rt, int stage, int* __restrict__ err) {
   extern __shared__ __align__(16) float sh[];
+  const int KS = KST ? KST : ks_rt;
   const int cols = RET_THREADS / KS * CV;
   const int dkp = KS * R;                   // dk rounded up to what the lanes of a column hold
   // two buffers of [stage][dkp] q, [stage][dkp] k, [stage][cols] v
@@ -125,7 +142,7 @@ __global__ void __launch_bounds__(RET_THREADS) retention_scan_kernel(
   }
 
   // A stage on its way into buffer `buf`: q and k rows by asynchronous 16-byte copies where
-  // the rows allow it, v (which changes type) through registers.
+  // the rows allow it, v (in float since the first kernel) by asynchronous copies of one.
   const int buf_elems = stage * (2 * dkp + cols);
   const bool rows16 = (dk & 3) == 0 && dkp == dk;
   auto issue = [&](int s0, int buf) {
@@ -157,11 +174,10 @@ __global__ void __launch_bounds__(RET_THREADS) retention_scan_kernel(
     }
     for (int idx = tid; idx < sn * cols; idx += RET_THREADS) {
       const int c = idx / cols, j = idx % cols;
-      float x = col0 + j < dv
-                    ? bf_ld(proj + (size_t)(t0 + s0 + c) * stride + v_off + (size_t)h * dv + col0 + j)
-                    : 0.f;
-      if (act) x = x / (1.f + expf(-x));
-      vd[idx] = x;
+      if (col0 + j < dv)
+        ret_cp4(vd + idx, vf + ((size_t)(t0 + s0 + c) * H + h) * dv + col0 + j);
+      else
+        vd[idx] = 0.f;
     }
     asm volatile("cp.async.commit_group;" ::);
   };
@@ -237,6 +253,7 @@ __global__ void __launch_bounds__(RET_THREADS) retention_scan_kernel(
 #undef RET_FETCH
 #undef RET_TOKEN
       // the KS partial sums of a column, all tokens of the chunk at a time
+#pragma unroll
       for (int o = 1; o < KS; o <<= 1) {
 #pragma unroll
         for (int c = 0; c < RET_CHUNK; ++c)
@@ -273,23 +290,23 @@ BF_EXPORT int bf_retention_scan(
     const void* proj, long long stride, long long q_off, long long k_off, long long v_off,
     const float* decays, const float* inv_freq, int rot_half, const int* positions, float* state,
     long long state_stride, const int* q_start, const int* state_slots, int n_slots, float* o_raw,
-    float* qk, int T, int B, int max_q, int H, int dk, int dv, float k_scale, int act_dtype,
-    int* err, int act, cudaStream_t stream) {
-  // qk: scratch, float [T][2][H][dk]; max_q: the most tokens one request brings (a hint that
+    float* qk, float* vf, int T, int B, int max_q, int H, int dk, int dv, float k_scale,
+    int act_dtype, int* err, int act, cudaStream_t stream) {
+  // qk: scratch, float [T][2][H][dk]; vf: scratch, float [T][H][dv]; max_q: the most tokens one request brings (a hint that
   // sizes the staging buffers: single tokens leave room for more blocks an SM)
   if (B <= 0 || T <= 0) return 0;
-  if (dk <= 0 || dv <= 0 || dk > 1024 || !qk) return (int)cudaErrorInvalidValue;
+  if (dk <= 0 || dv <= 0 || dk > 1024 || !qk || !vf) return (int)cudaErrorInvalidValue;
   {
     const int threads = 128;
     const long long blocks = ((long long)T * H * 32 + threads - 1) / threads;
     if (act_dtype == BF_DTYPE_F32)
       retention_encode_kernel<float><<<(unsigned)blocks, threads, 0, stream>>>(
           (const float*)proj, stride, q_off, k_off, inv_freq, rot_half, positions, qk, T, H, dk,
-          k_scale, act);
+          k_scale, act, v_off, dv, vf);
     else
       retention_encode_kernel<__nv_bfloat16><<<(unsigned)blocks, threads, 0, stream>>>(
           (const __nv_bfloat16*)proj, stride, q_off, k_off, inv_freq, rot_half, positions, qk, T,
-          H, dk, k_scale, act);
+          H, dk, k_scale, act, v_off, dv, vf);
     const int e = bf_launch_status();
     if (e) return e;
   }
@@ -309,25 +326,21 @@ BF_EXPORT int bf_retention_scan(
     stage >>= 1;
   const size_t smem = (size_t)2 * stage * (2 * KS * R + cols) * sizeof(float);
   if (smem > 200 * 1024) return (int)cudaErrorInvalidValue;
-#define RET_GO(AT, RR, CC)                                                                    \
+#define RET_GO(RR, CC, KK)                                                                    \
   {                                                                                            \
     if (smem > 48 * 1024)                                                                      \
-      cudaFuncSetAttribute(retention_scan_kernel<AT, RR, CC>,                                  \
+      cudaFuncSetAttribute(retention_scan_kernel<RR, CC, KK>,                                  \
                            cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);            \
-    retention_scan_kernel<AT, RR, CC><<<grid, RET_THREADS, smem, stream>>>(                    \
-        (const AT*)proj, stride, v_off, qk, decays, state, state_stride, q_start, state_slots, \
-        n_slots, o_raw, H, dk, dv, KS, stage, err, act);                                       \
+    retention_scan_kernel<RR, CC, KK><<<grid, RET_THREADS, smem, stream>>>(                    \
+        vf, qk, decays, state, state_stride, q_start, state_slots, n_slots, o_raw, H, dk, dv,  \
+        KS, stage, err);                                                                       \
   }
-#define RET_PICK(AT)                                             \
-  if (R == 32) RET_GO(AT, 32, 1)                                  \
-  else if (CV == 2) RET_GO(AT, 8, 2)                              \
-  else RET_GO(AT, 8, 1)
-  if (act_dtype == BF_DTYPE_F32) {
-    RET_PICK(float)
-  } else {
-    RET_PICK(__nv_bfloat16)
-  }
-#undef RET_PICK
+  if (R == 32) RET_GO(32, 1, 0)
+  else if (CV == 1) RET_GO(8, 1, 0)
+  else if (KS == 8) RET_GO(8, 2, 8)
+  else if (KS == 16) RET_GO(8, 2, 16)
+  else if (KS == 32) RET_GO(8, 2, 32)
+  else RET_GO(8, 2, 0)
 #undef RET_GO
   return bf_launch_status();
 }
