@@ -43,9 +43,11 @@ __device__ __forceinline__ void lat_load_tile(__nv_bfloat16* tile, int pitch,
                                               const int* __restrict__ table, int first, int last,
                                               int W, int page_size, int num_pages,
                                               int* __restrict__ err) {
+  // a warp a key row at a time: the page is looked up once per row, the lanes share the
+  // row's 16-byte pieces out
   const int chunks = W >> 3;
-  for (int i = threadIdx.x; i < LAT_KEYS * chunks; i += LAT_THREADS) {
-    const int r = i / chunks, c = (i - r * chunks) << 3;
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  for (int r = warp; r < LAT_KEYS; r += LAT_THREADS / 32) {
     const int e = first + r;
     bool ok = e <= last;
     const __nv_bfloat16* src = cache;
@@ -53,13 +55,15 @@ __device__ __forceinline__ void lat_load_tile(__nv_bfloat16* tile, int pitch,
       const int lp = e / page_size;
       const int page = table[lp];
       if (page < 0 || page >= num_pages) {
-        atomicOr(err, BF_ERR_PAGE);
+        if (lane == 0) atomicOr(err, BF_ERR_PAGE);
         ok = false;
       } else {
-        src = cache + ((size_t)page * page_size + (e - lp * page_size)) * W + c;
+        src = cache + ((size_t)page * page_size + (e - lp * page_size)) * W;
       }
     }
-    cp_async16(tile + (size_t)r * pitch + c, src, ok ? 16 : 0);
+    __nv_bfloat16* dst = tile + (size_t)r * pitch;
+    for (int c = lane; c < chunks; c += 32)
+      cp_async16(dst + 8 * c, ok ? src + 8 * c : cache, ok ? 16 : 0);
   }
 }
 
@@ -131,13 +135,34 @@ __global__ void __launch_bounds__(LAT_THREADS) latent_attention_kernel(
       const __nv_bfloat16* qa = Qs + (size_t)(mt * 16 + (lane & 15)) * pitch + (lane >> 4) * 8;
       const __nv_bfloat16* kb_ = Kt + (size_t)(qt * 16 + (lane & 7) + ((lane >> 4) << 3)) * pitch +
                                  ((lane >> 3) & 1) * 8;
-      for (int ks = 0; ks < W; ks += 16) {
+      // two sets of accumulators take alternate steps of 16 sizes, so that a product does
+      // not wait for the one before it; W is a multiple of 16, the odd last step goes to
+      // the first set
+      float s2[2][4] = {{0.f, 0.f, 0.f, 0.f}, {0.f, 0.f, 0.f, 0.f}};
+      int ks = 0;
+#pragma unroll 2
+      for (; ks + 32 <= W; ks += 32) {
+        unsigned a[4], kb[4], a2[4], kb2[4];
+        ldmatrix_x4(a, qa + ks);
+        ldmatrix_x4(kb, kb_ + ks);
+        ldmatrix_x4(a2, qa + ks + 16);
+        ldmatrix_x4(kb2, kb_ + ks + 16);
+        mma_bf16_16816(s[0], a, kb[0], kb[1]);
+        mma_bf16_16816(s[1], a, kb[2], kb[3]);
+        mma_bf16_16816(s2[0], a2, kb2[0], kb2[1]);
+        mma_bf16_16816(s2[1], a2, kb2[2], kb2[3]);
+      }
+      if (ks < W) {
         unsigned a[4], kb[4];
         ldmatrix_x4(a, qa + ks);
         ldmatrix_x4(kb, kb_ + ks);
         mma_bf16_16816(s[0], a, kb[0], kb[1]);
         mma_bf16_16816(s[1], a, kb[2], kb[3]);
       }
+#pragma unroll
+      for (int nt = 0; nt < 2; ++nt)
+#pragma unroll
+        for (int e = 0; e < 4; ++e) s[nt][e] += s2[nt][e];
     }
     // mask by each row's own position; the rows' maxima over this warp's keys
     float mx[2] = {-1e30f, -1e30f};
