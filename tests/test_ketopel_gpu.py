@@ -633,6 +633,33 @@ def test_greedy_generation_through_the_engine(cuda_device, tmp_path, graphs, ste
         assert getattr(eng.runner, "graph_replays", 0) > 0
 
 
+def test_command_line_generates_from_a_looped_folder(cuda_device, tmp_path, capsys):
+    """``bin/binfer``'s entry point on a looped folder: the registry picks the family from
+    config.json; greedy tokens are the plain implementation's, and sampling with a seed
+    gives the same tokens twice."""
+    from binfer_b200.cli import main
+    d = H.make_ketopel_dir(tmp_path, "C")
+    raw, w = H.read_model_dir(d)
+    prompt = H.random_tokens(9, raw["vocab"], 3)
+    ids = ",".join(map(str, prompt))
+    rc = main([d, "--prompt-ids", ids, "--max-tokens", "5", "--dtype", "fp32", "--ignore-eos",
+               "-q", "--kv-pages", "32"])
+    assert rc == 0
+    out = [int(t) for t in capsys.readouterr().out.split()]
+    assert len(out) == 5
+    logits = P.forward(raw, w, list(prompt) + out)
+    for n, tok in enumerate(out):
+        row = logits[len(prompt) - 1 + n]
+        assert float(row[tok]) >= float(row.max()) - 1e-4 * float(row.abs().max())
+    sampled = []
+    for _ in range(2):
+        rc = main([d, "--prompt-ids", ids, "--max-tokens", "8", "--dtype", "fp32", "--ignore-eos",
+                   "-q", "--kv-pages", "32", "--temperature", "0.9", "--seed", "5"])
+        assert rc == 0
+        sampled.append(capsys.readouterr().out.split())
+    assert sampled[0] == sampled[1] and len(sampled[0]) == 8
+
+
 def test_trace_replay_tool_with_four_state_slots(cuda_device, tmp_path):
     """``bin/trace_run`` as a user runs it on a looped model: six requests through its four
     state slots and a page pool sized by ``--max-tokens``."""
