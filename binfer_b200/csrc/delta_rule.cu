@@ -83,8 +83,9 @@ __global__ void __launch_bounds__(DR_THREADS) delta_scan_kernel(
   }
 
   // one buffer: [stage][dkp] q, [stage][dkp] k, [stage][cols] v, [stage][2] beta and decay,
-  // [stage] k . q
-  const int buf_elems = stage * (2 * dkp + cols + 3);
+  // [stage] k . q; a buffer is a whole number of 16-byte pieces long, so that the second one
+  // starts on such a boundary too
+  const int buf_elems = (stage * (2 * dkp + cols + 3) + 3) & ~3;
   const bool rows16 = (dk & 3) == 0 && (C & 3) == 0;
   auto issue = [&](int s0, int buf) {
     const int sn = min(stage, n - s0);
@@ -239,7 +240,8 @@ BF_EXPORT int bf_delta_scan(const float* qkv, const float* gates, float* state,
   int stage = 32;
   while (stage > 2 && stage / 2 >= max_q) stage >>= 1;
   while (stage > 2 && 2 * stage * per_token > 64 * 1024) stage >>= 1;
-  const size_t smem = 2 * stage * per_token;
+  // as the kernel lays it out: two buffers, each rounded up to 16 bytes
+  const size_t smem = 2 * ((stage * per_token + 15) & ~(size_t)15);
   dim3 grid((dv + cols - 1) / cols, H, B);
 #define DR_GO(RR, KK)                                                                          \
   {                                                                                            \

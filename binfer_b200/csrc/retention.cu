@@ -322,7 +322,8 @@ BF_EXPORT int bf_retention_scan(
   dim3 grid((dv + cols - 1) / cols, H, B);
   int stage = RET_STAGE;
   while (stage > RET_CHUNK && stage / 2 >= max_q) stage >>= 1;
-  while (stage > RET_CHUNK && (size_t)2 * stage * (2 * KS * R + cols) * sizeof(float) > 72 * 1024)
+  // (keys beyond 512 a head: fewer tokens a stage than a chunk holds; the walk takes what is there)
+  while (stage > 4 && (size_t)2 * stage * (2 * KS * R + cols) * sizeof(float) > 72 * 1024)
     stage >>= 1;
   const size_t smem = (size_t)2 * stage * (2 * KS * R + cols) * sizeof(float);
   if (smem > 200 * 1024) return (int)cudaErrorInvalidValue;

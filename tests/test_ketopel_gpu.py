@@ -132,7 +132,7 @@ def test_gated_norm_of_a_recurrence_output(cuda_device, heads, dv, over_all, sha
 # ------------------------------------------------------------------ mechanisms alone
 @pytest.mark.parametrize("heads,kv_heads,dk,dv,conv", [
     (2, 1, 16, 32, 3), (1, 1, 40, 24, 4), (3, 3, 8, 8, 1), (2, 2, 72, 96, 2), (2, 1, 136, 20, 2),
-    (1, 1, 6, 300, 5), (4, 2, 128, 64, 4)])
+    (1, 1, 6, 300, 5), (4, 2, 128, 64, 4), (2, 1, 320, 12, 2), (1, 1, 600, 8, 3)])
 def test_delta_rule_alone(cuda_device, tmp_path, heads, kv_heads, dk, dv, conv):
     """One layer: a prompt at once, portions, and token by token, over 200 tokens, with a
     decay close to one on the first head, so that the first tokens' writes still count at
@@ -154,7 +154,7 @@ def test_delta_rule_alone(cuda_device, tmp_path, heads, kv_heads, dk, dv, conv):
 
 @pytest.mark.parametrize("heads,dk,dv,decay", [
     (2, 16, 32, (0.9, 0.999)), (1, 40, 24, (1.0,)), (3, 8, 8, (0.5, 0.98, 0.75)),
-    (2, 72, 96, (0.97, 0.99)), (1, 264, 40, (0.99,)), (1, 6, 300, (0.98,))])
+    (2, 72, 96, (0.97, 0.99)), (1, 264, 40, (0.99,)), (1, 6, 300, (0.98,)), (1, 600, 8, (0.99,))])
 def test_lightning_attention_alone(cuda_device, tmp_path, heads, dk, dv, decay):
     """One layer whose softmax branch counts for nothing."""
     layer = H._ket_parallel(H._ket_left(2, 1, 8, 8, 4), H._ket_right(heads, dk, dv, decay),
