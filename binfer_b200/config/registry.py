@@ -73,6 +73,8 @@ def _register_builtin() -> None:
     register_architecture("Fikotar", FikotarConfig.from_dict)
     from .ketopel import KetopelConfig
     register_architecture("Ketopel", KetopelConfig.from_dict)
+    from .folivik import FolivikConfig
+    register_architecture("Folivik", FolivikConfig.from_dict)
 
 
 _register_builtin()

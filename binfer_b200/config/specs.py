@@ -74,6 +74,8 @@ class NormSpec:
     offset: float = 0.0
     # layernorm: what follows the weight tensor's name to give the bias tensor's (None: no bias)
     bias_suffix: Optional[str] = None
+    # rmsnorm: the weight tensor is a single number that multiplies every coordinate
+    scalar_weight: bool = False
 
 
 @dataclass(frozen=True)
@@ -203,7 +205,13 @@ class ConvWindowAttentionSpec:
     sees j <= i with ``i - j < window`` or ``j < keep_first``; ``window`` None: every j <= i),
     softmax whose denominator also holds ``exp(sink_h)`` when ``sinks``, values of size
     ``value_dim``, output projection.  ``names``: the tensors inside the mixer's prefix;
-    a convolution's tensor is the projection's name with ``conv_suffix``."""
+    a convolution's tensor is the projection's name with ``conv_suffix``.
+
+    ``head_norm_weight``: the norm of each q and k head (``unit_norm``) is followed by a weight
+    of ``head_dim`` numbers that the heads share (tensors ``q_head_norm``, ``k_head_norm``).
+    ``head_temperature``: head h's scores are multiplied by the number ``temp[h]`` (a tensor of
+    the mixer).  ``log_distance_bias``: ``b1_h ln(1 + b2_h (i - j))`` is taken off the score of
+    query i and key j (tensors ``bias_slope`` b1 and ``bias_rate`` b2, one number per head)."""
 
     kind: str = "conv_window_attention"
     num_heads: int = 0
@@ -220,9 +228,14 @@ class ConvWindowAttentionSpec:
     sinks: bool = False
     proj_norm: bool = False
     softcap: float = 0.0
+    head_norm_weight: bool = False
+    head_temperature: bool = False
+    log_distance_bias: bool = False
     names: Tuple[Tuple[str, str], ...] = (("q", "q"), ("k", "k"), ("v", "v"), ("o", "o"),
                                           ("sink", "sink"), ("q_norm", "q.norm"),
-                                          ("k_norm", "k.norm"))
+                                          ("k_norm", "k.norm"), ("q_head_norm", "q.norm"),
+                                          ("k_head_norm", "k.norm"), ("temp", "temp"),
+                                          ("bias_slope", "r1"), ("bias_rate", "r2"))
     conv_suffix: str = ".conv"
 
     @property
@@ -268,7 +281,9 @@ class LatentAttentionSpec:
     ``value_dim`` numbers.  Only c and the shared part are cached.  ``head_gate``: head h's
     output is multiplied by the sigmoid of a projection of the mixer's input to one number
     per head.  ``position``: the rotation of the ``rot_dim`` parts (layout and offset are
-    set by the mixer).  ``names``: the tensors inside the mixer's prefix."""
+    set by the mixer).  ``q_rank`` > 0: the queries go through a latent too, ``q = W_uq
+    rmsnorm(W_dq h)`` with a weight of ``q_rank`` numbers (tensors ``dq``, ``dq_norm``, ``uq``
+    in place of ``q``).  ``names``: the tensors inside the mixer's prefix."""
 
     kind: str = "latent_attention"
     num_heads: int = 0
@@ -280,8 +295,10 @@ class LatentAttentionSpec:
     norm_eps: float = 1e-6
     position: Optional[RopeSpec] = None
     head_gate: bool = True
+    q_rank: int = 0
     names: Tuple[Tuple[str, str], ...] = (("q", "q"), ("dkv", "dkv"), ("dkv_norm", "dkv.norm"),
-                                          ("uk", "uk"), ("uv", "uv"), ("g", "g"), ("o", "o"))
+                                          ("uk", "uk"), ("uv", "uv"), ("g", "g"), ("o", "o"),
+                                          ("dq", "dq"), ("dq_norm", "dq.norm"), ("uq", "uq"))
 
     @property
     def softmax_scale(self) -> float:
@@ -318,6 +335,36 @@ class GatedDeltaRuleSpec:
 
 
 @dataclass(frozen=True)
+class Mamba2Spec:
+    """A selective state space layer in its scalar-decay form (Mamba-2).  One input projection
+    yields ``[z | x | B | C | dt]``: ``inner = num_heads * head_dim`` numbers each for the gate
+    z and the input x, ``groups * state_dim`` each for B and C, one step size per head.  x, B
+    and C pass a causal convolution of ``conv_taps`` taps per channel (with a bias when
+    ``conv_bias``) and ``silu``.  Per head h, which reads group ``h // (num_heads / groups)``,
+    with a state ``S [state_dim, head_dim]`` that starts at zero::
+
+        dt = softplus(dt + dt_bias_h);   S <- exp(-exp(A_log_h) dt) S + dt B x^T
+        y = S^T C + D_h x
+
+    The concatenated heads are multiplied by ``silu(z)``, then RMS-normed in ``norm_groups``
+    equal parts (each by its own root mean square, ``norm_eps``), times a weight of ``inner``
+    numbers, and projected.  ``names``: the tensors inside the mixer's prefix."""
+
+    kind: str = "mamba2"
+    num_heads: int = 0
+    head_dim: int = 0
+    state_dim: int = 0
+    groups: int = 1
+    conv_taps: int = 0
+    conv_bias: bool = True
+    norm_groups: int = 1
+    norm_eps: float = 1e-6
+    names: Tuple[Tuple[str, str], ...] = (
+        ("in", "in"), ("conv", "conv"), ("conv_bias", "conv.b"), ("dt_bias", "dt_bias"),
+        ("A_log", "A_log"), ("D", "D"), ("norm", "norm"), ("o", "o"))
+
+
+@dataclass(frozen=True)
 class MixerBranch:
     """One of the mixers that run side by side: its spec, the name that follows the
     combined mixer's prefix (``left.``), and the factor of its output in the sum."""
@@ -342,7 +389,16 @@ class MoESpec:
     (``shared_size`` > 0) runs for every token, multiplied by the sigmoid of a projection of
     its own to one number when ``shared_gate``.  Names inside the feed-forward's prefix:
     ``expert_prefix.format(e=...)`` and ``shared_prefix`` before ``names`` (gate, up, down);
-    ``router_name``; ``shared_gate_name`` inside the shared expert's prefix."""
+    ``router_name``; ``shared_gate_name`` inside the shared expert's prefix.
+
+    ``scoring`` "softmax_all": the scores are the softmax over every router output instead, and
+    the chosen experts' weights are their scores divided by their sum (plus ``weight_eps``),
+    times ``route_scale``.  ``correction``: a tensor (``correction_name``, one number per
+    router output) is added to the scores for the choice only.  ``groups`` > 1: the router's
+    outputs form that many equal groups of neighbours, a group counts by its largest choice
+    score, and only the outputs of the best ``groups_keep`` groups can be chosen.
+    ``identity`` > 0: the router has that many outputs behind the experts' that stand for
+    experts whose output is their input (no tensors)."""
 
     kind: str = "moe"
     num_experts: int = 0
@@ -356,6 +412,14 @@ class MoESpec:
     shared_prefix: str = "shared."
     router_name: str = "router"
     shared_gate_name: str = "sg"
+    scoring: str = "softmax_top"
+    route_scale: float = 1.0
+    weight_eps: float = 0.0
+    correction: bool = False
+    correction_name: str = "correction"
+    groups: int = 1
+    groups_keep: int = 1
+    identity: int = 0
 
 
 @dataclass(frozen=True)

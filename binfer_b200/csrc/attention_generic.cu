@@ -18,7 +18,9 @@
 // It is also where changes to the scores live, for attention that has them (the tuned
 // kernels take none): a soft cap s <- c tanh(s / c), a bias per distance s <- s +
 // slope_h (j - p), and a sink, a logit per head that joins the softmax's denominator and
-// carries no value.  All three are off with softcap 0 and null pointers.
+// carries no value.  All three are off with softcap 0 and null pointers.  One more bias per
+// distance grows with its logarithm: s <- s - b1_h ln(1 + b2_h (p - j)) (`log_slope` b1 and
+// `log_rate` b2, one number per query head; off with null pointers).
 //
 // Two more things that the tuned kernels do not take: values of another size than keys
 // (`dv`), and a window that keeps the request's first tokens: with keep_first > 0 the keys
@@ -43,7 +45,7 @@ __global__ void paged_attention_generic_kernel(
     int d, int page_size, int num_pages, int window, float scale, float softcap,
     const float* __restrict__ slopes, const float* __restrict__ sinks, int* __restrict__ err,
     int dv, int keep_first, long long q_stride, long long out_stride, float out_scale,
-    long long v_stride) {
+    long long v_stride, const float* __restrict__ log_slope, const float* __restrict__ log_rate) {
   extern __shared__ float sh[];
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
   const int warps = blockDim.x >> 5;
@@ -94,6 +96,7 @@ __global__ void paged_attention_generic_kernel(
       for (int i = 0; i < d; ++i) a += qs[i] * bf_ld(kr + i);
       if (softcap > 0.f) a = softcap * tanhf(a / softcap);
       if (slopes) a += slopes[h] * (float)(j - p);
+      if (log_slope) a -= log_slope[h] * log1pf(log_rate[h] * (float)(p - j));
       s = a;
     }
     const float m_new = fmaxf(m, warp_max(s));
@@ -138,10 +141,11 @@ BF_EXPORT int bf_paged_attention_generic(
     int nkv, int d, int page_size, int num_pages, int window, float scale, float softcap,
     const float* slopes, const float* sinks, int act_dtype, int* err, int dv, int keep_first,
     long long q_stride, long long out_stride, float out_scale, long long v_stride,
-    cudaStream_t stream) {
+    const float* log_slope, const float* log_rate, cudaStream_t stream) {
   if (T <= 0) return 0;
   if (d > ATT_MAX_D || dv > 512 || nkv <= 0 || nh % nkv) return (int)cudaErrorInvalidValue;
   if (v_stride <= 0) v_stride = dv;
+  if (!log_slope || !log_rate) log_slope = log_rate = nullptr;
   const int warps = 4;
   dim3 grid(T, (nh + warps - 1) / warps);
   const size_t smem = (size_t)warps * d * sizeof(float);
@@ -149,7 +153,8 @@ BF_EXPORT int bf_paged_attention_generic(
   paged_attention_generic_kernel<AT, ACC><<<grid, warps * 32, smem, stream>>>(                 \
       (const AT*)q, (const AT*)k_cache, (const AT*)v_cache, seq_of_token, positions,           \
       block_tables, table_stride, (AT*)out, nh, nkv, d, page_size, num_pages, window, scale,   \
-      softcap, slopes, sinks, err, dv, keep_first, q_stride, out_stride, out_scale, v_stride)
+      softcap, slopes, sinks, err, dv, keep_first, q_stride, out_stride, out_scale, v_stride,  \
+      log_slope, log_rate)
   if (act_dtype == BF_DTYPE_F32) {
     if (dv <= 256) ATT_GO(float, 8); else ATT_GO(float, 16);
   } else {

@@ -5,7 +5,10 @@
 // and no state; rot_half 0: no rotation; unit_norm 0: no norm).  Between the convolution and
 // the rotation q and k may be multiplied by a factor per token (`pre_factor` [T][2]: q, k) and a
 // weight per channel (`pre_weight`): an RMS norm over a whole projection, whose factor a kernel
-// in front has taken.  The cosines and sines are multiplied by `rot_mag`.
+// in front has taken.  The cosines and sines are multiplied by `rot_mag`.  After the norm of the
+// heads q and k may be multiplied by a weight per size of a head that the heads share (`head_w`
+// [2][dk]: q's, then k's), and each q head by a number of its own (`q_head_scale` [nh]: a factor
+// on the head's scores).
 //
 //   y_t[c] = sum_j w[c, j] * u_{t - taps + 1 + j}[c],   j = 0 .. taps-1
 //
@@ -60,7 +63,8 @@ __global__ void conv_encode_kernel(
     A* __restrict__ q_out, long long q_stride, A* __restrict__ k_cache, A* __restrict__ v_cache,
     int T, int nh, int nkv, int dk, int dv, int page_size, long long num_slots, int unit_norm,
     float eps, int vec2, int hpw, int* __restrict__ err, const float* __restrict__ pre_factor,
-    const float* __restrict__ pre_weight) {
+    const float* __restrict__ pre_weight, const float* __restrict__ head_w,
+    const float* __restrict__ q_head_scale) {
   extern __shared__ float sh[];
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
   const int heads_total = nh + 2 * nkv;
@@ -151,6 +155,11 @@ __global__ void conv_encode_kernel(
   __syncwarp();
   float f = 1.f;
   if (kind < 2 && unit_norm) f = rsqrtf(warp_sum(ss) / (float)d + eps);
+  if (kind < 2 && head_w) {                    // the weight behind the heads' norm
+    for (int i = lane; i < d; i += 32) res[i] *= head_w[kind * dk + i];
+    __syncwarp();
+  }
+  if (kind == 0 && q_head_scale) f *= q_head_scale[head];
   if (kind == 0) {
     A* o = q_out + (size_t)t * q_stride + (size_t)head * dk;
     if (vec2 && (q_stride & 1) == 0)
@@ -178,7 +187,8 @@ BF_EXPORT int bf_conv_encode(
     const int* slots, void* q_out, long long q_stride, void* k_cache, void* v_cache, int T,
     int nh, int nkv, int dk, int dv, int page_size, long long num_slots, int unit_norm, float eps,
     int act_dtype, float* rope_table, int* err, const float* pre_factor,
-    const float* pre_weight, float rot_mag, cudaStream_t stream) {
+    const float* pre_weight, float rot_mag, const float* head_w, const float* q_head_scale,
+    cudaStream_t stream) {
   // rope_table: scratch, float [T][rot_half][2] (unused without a rotation)
   if (T <= 0) return 0;
   if (taps > CE_MAX_TAPS || (taps > 1 && !state)) return (int)cudaErrorInvalidValue;
@@ -210,14 +220,14 @@ BF_EXPORT int bf_conv_encode(
         (const float*)proj, stride, conv_w, taps, state, state_stride, state_slots, n_state_slots,
         seq_of_token, q_start, (const float2*)rope_table, rot_half, slots, (float*)q_out,
         q_stride, (float*)k_cache, (float*)v_cache, T, nh, nkv, dk, dv, page_size, num_slots,
-        unit_norm, eps, vec2, hpw, err, pre_factor, pre_weight);
+        unit_norm, eps, vec2, hpw, err, pre_factor, pre_weight, head_w, q_head_scale);
   else
     conv_encode_kernel<__nv_bfloat16><<<blocks, warps * 32, smem, stream>>>(
         (const __nv_bfloat16*)proj, stride, conv_w, taps, state, state_stride, state_slots,
         n_state_slots, seq_of_token, q_start, (const float2*)rope_table, rot_half, slots,
         (__nv_bfloat16*)q_out, q_stride, (__nv_bfloat16*)k_cache, (__nv_bfloat16*)v_cache, T, nh,
         nkv, dk, dv, page_size, num_slots, unit_norm, eps, vec2, hpw, err, pre_factor,
-        pre_weight);
+        pre_weight, head_w, q_head_scale);
   return bf_launch_status();
 }
 

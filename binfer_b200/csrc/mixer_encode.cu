@@ -3,6 +3,8 @@
 //
 //   section_rms      rsqrt(mean(x^2) + eps) of two column sections of every row: the factor
 //                    of an RMS norm over a whole projection (all heads at once)
+//   section_norm     an RMS norm with a weight over one column section of every row, into a
+//                    buffer of its own (a latent between two products)
 //   latent_encode    attention over a cached latent: the latent's norm, the rotation of the
 //                    shared key part and of every query head's rotated part, the latent and
 //                    the key part into the cache pages
@@ -54,8 +56,43 @@ BF_EXPORT int bf_section_rms(const void* x, long long stride, int off0, int n0, 
   return bf_launch_status();
 }
 
+// ------------------------------------------------------------------- section_norm
+// out[t, i] = x[t, off + i] * rsqrt(mean_i x[t, off + i]^2 + eps) * w[i], one block per row.
+template <typename A>
+__global__ void section_norm_kernel(const A* __restrict__ x, long long stride, long long off,
+                                    int n, const float* __restrict__ w, float eps,
+                                    A* __restrict__ out, long long out_stride) {
+  __shared__ float scratch[33];
+  const int t = blockIdx.x;
+  const A* row = x + (size_t)t * stride + off;
+  float ss = 0.f;
+  for (int i = threadIdx.x; i < n; i += blockDim.x) {
+    const float v = bf_ld(row + i);
+    ss += v * v;
+  }
+  ss = block_sum(ss, scratch);
+  const float f = rsqrtf(ss / (float)n + eps);
+  A* o = out + (size_t)t * out_stride;
+  for (int i = threadIdx.x; i < n; i += blockDim.x) bf_st(o + i, bf_ld(row + i) * f * w[i]);
+}
+
+BF_EXPORT int bf_section_norm(const void* x, long long stride, long long off, int n,
+                              const float* w, float eps, void* out, long long out_stride, int T,
+                              int act_dtype, cudaStream_t stream) {
+  if (T <= 0 || n <= 0) return 0;
+  const int threads = n > 2048 ? 256 : 128;
+  if (act_dtype == BF_DTYPE_F32)
+    section_norm_kernel<float><<<T, threads, 0, stream>>>((const float*)x, stride, off, n, w, eps,
+                                                         (float*)out, out_stride);
+  else
+    section_norm_kernel<__nv_bfloat16><<<T, threads, 0, stream>>>(
+        (const __nv_bfloat16*)x, stride, off, n, w, eps, (__nv_bfloat16*)out, out_stride);
+  return bf_launch_status();
+}
+
 // ------------------------------------------------------------------ latent_encode
-// A row of `proj` holds [q: H heads of (d plain | dr rotated)] from q_off and, from kv_off,
+// A row of `q` holds [H heads of (d plain | dr rotated)] (rows `q_stride` apart: a column block
+// of `proj` or a buffer of its own) and a row of `proj`, from kv_off,
 // [rank numbers that become the latent | dr numbers that become the shared key part].
 // The cache row of a token is [latent (normed, weighted) | key part (rotated)], one "head" of
 // rank + dr numbers.  q_abs [T, H, rank + dr] gets only every head's rotated part, at
@@ -63,7 +100,8 @@ BF_EXPORT int bf_section_rms(const void* x, long long stride, int off0, int n0, 
 // One block per token.
 template <typename A>
 __global__ void latent_encode_kernel(
-    const A* __restrict__ proj, long long stride, long long q_off, long long kv_off,
+    const A* __restrict__ proj, long long stride, const A* __restrict__ q, long long q_stride,
+    long long kv_off,
     const float* __restrict__ norm_w, float eps, const float* __restrict__ inv_freq,
     int rot_half, int interleaved, float rot_mag, const int* __restrict__ positions,
     const int* __restrict__ slots, A* __restrict__ q_abs, A* __restrict__ cache, int H, int d,
@@ -112,7 +150,7 @@ __global__ void latent_encode_kernel(
   }
   for (int idx = threadIdx.x; idx < H * rot_half; idx += blockDim.x) {
     const int h = idx / rot_half, m = idx - h * rot_half;
-    const A* qr = row + q_off + (size_t)h * (d + dr) + d;
+    const A* qr = q + (size_t)t * q_stride + (size_t)h * (d + dr) + d;
     A* o = q_abs + ((size_t)t * H + h) * W + rank;
     int a, b;
     me_pair(m, rot_half, interleaved, &a, &b);
@@ -124,12 +162,13 @@ __global__ void latent_encode_kernel(
   for (int idx = threadIdx.x; idx < H * rest; idx += blockDim.x) {
     const int h = idx / rest, i = 2 * rot_half + idx % rest;
     bf_st(q_abs + ((size_t)t * H + h) * W + rank + i,
-          bf_ld(row + q_off + (size_t)h * (d + dr) + d + i));
+          bf_ld(q + (size_t)t * q_stride + (size_t)h * (d + dr) + d + i));
   }
 }
 
-BF_EXPORT int bf_latent_encode(const void* proj, long long stride, long long q_off,
-                               long long kv_off, const float* norm_w, float eps,
+BF_EXPORT int bf_latent_encode(const void* proj, long long stride, const void* q,
+                               long long q_stride, long long kv_off, const float* norm_w,
+                               float eps,
                                const float* inv_freq, int rot_half, int interleaved,
                                float rot_mag, const int* positions, const int* slots, void* q_abs,
                                void* cache, int T, int H, int d, int dr, int rank, int page_size,
@@ -141,14 +180,14 @@ BF_EXPORT int bf_latent_encode(const void* proj, long long stride, long long q_o
   const size_t smem = (size_t)(2 * rot_half + 33) * sizeof(float);
   if (act_dtype == BF_DTYPE_F32)
     latent_encode_kernel<float><<<T, threads, smem, stream>>>(
-        (const float*)proj, stride, q_off, kv_off, norm_w, eps, inv_freq, rot_half, interleaved,
-        rot_mag, positions, slots, (float*)q_abs, (float*)cache, H, d, dr, rank, page_size,
-        num_slots, err);
+        (const float*)proj, stride, (const float*)q, q_stride, kv_off, norm_w, eps, inv_freq,
+        rot_half, interleaved, rot_mag, positions, slots, (float*)q_abs, (float*)cache, H, d, dr,
+        rank, page_size, num_slots, err);
   else
     latent_encode_kernel<__nv_bfloat16><<<T, threads, smem, stream>>>(
-        (const __nv_bfloat16*)proj, stride, q_off, kv_off, norm_w, eps, inv_freq, rot_half,
-        interleaved, rot_mag, positions, slots, (__nv_bfloat16*)q_abs, (__nv_bfloat16*)cache, H,
-        d, dr, rank, page_size, num_slots, err);
+        (const __nv_bfloat16*)proj, stride, (const __nv_bfloat16*)q, q_stride, kv_off, norm_w,
+        eps, inv_freq, rot_half, interleaved, rot_mag, positions, slots, (__nv_bfloat16*)q_abs,
+        (__nv_bfloat16*)cache, H, d, dr, rank, page_size, num_slots, err);
   return bf_launch_status();
 }
 

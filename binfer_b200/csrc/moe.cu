@@ -7,6 +7,15 @@
 // with a shared expert that has a gate of its own, row E of the router matrix is that gate's
 // weight vector and column E receives sigmoid(w_sg . h).
 //
+// The router has a second way of scoring (`mode` 1): the scores are the softmax over all of
+// the router's outputs; a correction per output is added for the choice only; with groups the
+// outputs form `n_groups` equal groups of neighbours, a group counts by its largest choice
+// score and only the outputs of the best `keep` groups can be chosen; the chosen outputs'
+// weights are their scores over their sum (+ weight_eps), times route_scale.  The last
+// `identity` of the router's outputs stand for experts that return their input: their weights
+// are added up in a column of their own behind the experts' (and the shared gate's), and
+// bf_moe_identity_add adds input times that column to the mixture's output.
+//
 // moe_act: for experts whose gate and up projections are stacked into one product
 // `gu [T, 2F]` (gate rows of all experts, then up rows; F = E ff + ff_shared), the
 // activations of every expert scaled by the token's weight for that expert,
@@ -28,16 +37,21 @@ template <typename A>
 __global__ void __launch_bounds__(MR_WARPS * 32) moe_route_kernel(
     const A* __restrict__ h, long long stride, const float* __restrict__ w, int T, int width,
     int E, int top, int shared_gate, int tokens_per_block, float* __restrict__ route_w,
-    int* __restrict__ top_ids, float* __restrict__ top_w) {
+    int* __restrict__ top_ids, float* __restrict__ top_w, int mode,
+    const float* __restrict__ correction, int n_groups, int keep, int identity,
+    float route_scale, float weight_eps) {
   extern __shared__ __align__(16) float sh[];
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
   const int t0 = blockIdx.x * tokens_per_block;
   const int nt = min(tokens_per_block, T - t0);
-  const int rows = E + (shared_gate ? 1 : 0);
+  const int R = E + identity;                      // the router's outputs that can be chosen
+  const int rows = R + (shared_gate ? 1 : 0);
+  const int rw_cols = E + (shared_gate ? 1 : 0) + (identity ? 1 : 0);
   const int wp = (width + 3) & ~3;
   float* x = sh;                                   // [MR_TOKENS][wp]
   float* part = sh + (size_t)MR_TOKENS * wp;       // [MR_WARPS][MR_TOKENS][rows]
   float* zs = part + (size_t)MR_WARPS * MR_TOKENS * rows;   // [MR_TOKENS][rows]
+  float* chs = zs + (size_t)MR_TOKENS * rows;      // [MR_TOKENS][rows]: choice scores (mode 1)
   for (int k = 0; k < nt; ++k) {
     const A* src = h + (size_t)(t0 + k) * stride;
 #pragma unroll 8
@@ -104,10 +118,93 @@ __global__ void __launch_bounds__(MR_WARPS * 32) moe_route_kernel(
   if (warp >= nt) return;
   const int t = t0 + warp;
   float* z = zs + (size_t)warp * rows;
-  float* rw = route_w + (size_t)t * rows;
-  for (int e = lane; e < rows; e += 32) rw[e] = 0.f;
-  if (shared_gate && lane == 0) rw[E] = 1.f / (1.f + expf(-z[E]));
+  float* rw = route_w + (size_t)t * rw_cols;
+  for (int e = lane; e < rw_cols; e += 32) rw[e] = 0.f;
+  if (shared_gate && lane == 0) rw[E] = 1.f / (1.f + expf(-z[R]));
   __syncwarp();
+  if (mode == 1) {
+    float* ch = chs + (size_t)warp * rows;
+    // this warp's slice of the partial sums' place, which nobody reads any more
+    float* gsc = part + (size_t)warp * MR_TOKENS * rows;   // [n_groups] scores, [n_groups] kept
+    float zmax = -FLT_MAX;
+    for (int e = lane; e < R; e += 32) zmax = fmaxf(zmax, z[e]);
+    zmax = warp_max(zmax);
+    float den = 0.f;
+    for (int e = lane; e < R; e += 32) den += expf(z[e] - zmax);
+    den = warp_sum(den);
+    for (int e = lane; e < R; e += 32) {
+      const float sc = expf(z[e] - zmax) / den;
+      z[e] = sc;
+      ch[e] = sc + (correction ? correction[e] : 0.f);
+    }
+    __syncwarp();
+    if (n_groups > 1) {
+      const int per = R / n_groups;
+      for (int g = lane; g < n_groups; g += 32) {
+        float best = -FLT_MAX;
+        for (int i = 0; i < per; ++i) best = fmaxf(best, ch[g * per + i]);
+        gsc[g] = best;
+        gsc[n_groups + g] = 0.f;
+      }
+      __syncwarp();
+      for (int k = 0; k < keep; ++k) {
+        float best = -FLT_MAX;
+        int at = 0x7fffffff;
+        for (int g = lane; g < n_groups; g += 32)
+          if (gsc[n_groups + g] == 0.f && (gsc[g] > best || at == 0x7fffffff)) {
+            best = gsc[g];
+            at = g;
+          }
+#pragma unroll
+        for (int o = 16; o > 0; o >>= 1) {
+          const float ob = __shfl_xor_sync(0xffffffffu, best, o);
+          const int oa = __shfl_xor_sync(0xffffffffu, at, o);
+          if (oa != 0x7fffffff && (at == 0x7fffffff || ob > best || (ob == best && oa < at))) {
+            best = ob;
+            at = oa;
+          }
+        }
+        if (lane == 0 && at != 0x7fffffff) gsc[n_groups + at] = 1.f;
+        __syncwarp();
+      }
+      for (int e = lane; e < R; e += 32)
+        if (gsc[n_groups + e / per] == 0.f) ch[e] = -FLT_MAX;
+      __syncwarp();
+    }
+    float sum = 0.f;
+    for (int k = 0; k < top; ++k) {
+      float best = -FLT_MAX;
+      int at = 0x7fffffff;
+      for (int e = lane; e < R; e += 32)
+        if (ch[e] > best) { best = ch[e]; at = e; }
+#pragma unroll
+      for (int o = 16; o > 0; o >>= 1) {
+        const float ob = __shfl_xor_sync(0xffffffffu, best, o);
+        const int oa = __shfl_xor_sync(0xffffffffu, at, o);
+        if (ob > best || (ob == best && oa < at)) { best = ob; at = oa; }
+      }
+      if (at == 0x7fffffff) at = 0;             // (fewer outputs left than `top`: not reached)
+      const float sc = z[at];
+      sum += sc;
+      if (lane == 0) {
+        top_ids[(size_t)t * top + k] = at;
+        top_w[(size_t)t * top + k] = sc;
+        ch[at] = -FLT_MAX;
+      }
+      __syncwarp();
+    }
+    const float f = route_scale / (sum + weight_eps);
+    if (lane == 0) {
+      for (int k = 0; k < top; ++k) {
+        const float pw = top_w[(size_t)t * top + k] * f;
+        const int id = top_ids[(size_t)t * top + k];
+        top_w[(size_t)t * top + k] = pw;
+        if (id < E) rw[id] = pw;
+        else rw[rw_cols - 1] += pw;
+      }
+    }
+    return;
+  }
   // the `top` largest, one after the other; the first is the softmax's maximum
   float zmax = 0.f, den = 0.f;
   for (int k = 0; k < top; ++k) {
@@ -143,14 +240,20 @@ __global__ void __launch_bounds__(MR_WARPS * 32) moe_route_kernel(
 
 BF_EXPORT int bf_moe_route(const void* h, long long stride, const float* w, int T, int width,
                            int E, int top, int shared_gate, float* route_w, int* top_ids,
-                           float* top_w, int act_dtype, cudaStream_t stream) {
+                           float* top_w, int act_dtype, int mode, const float* correction,
+                           int n_groups, int keep, int identity, float route_scale,
+                           float weight_eps, cudaStream_t stream) {
   if (T <= 0) return 0;
-  if (top < 1 || top > E) return (int)cudaErrorInvalidValue;
-  const int rows = E + (shared_gate ? 1 : 0);
+  if (mode == 0) { identity = 0; n_groups = 1; correction = nullptr; }
+  if (n_groups < 1) n_groups = 1;
+  if (top < 1 || top > E + identity || identity < 0 || (E + identity) % n_groups ||
+      keep < 1 || keep > n_groups || top > keep * ((E + identity) / n_groups))
+    return (int)cudaErrorInvalidValue;
+  const int rows = E + identity + (shared_gate ? 1 : 0);
   // few tokens: one a block, so that the step's blocks are many; else a router row serves four
   const int tpb = T >= 4 * 148 ? MR_TOKENS : 1;
   const size_t smem = ((size_t)MR_TOKENS * ((width + 3) & ~3) +
-                       (size_t)(MR_WARPS + 1) * MR_TOKENS * rows) * sizeof(float);
+                       (size_t)(MR_WARPS + 2) * MR_TOKENS * rows) * sizeof(float);
   if (smem > 200 * 1024) return (int)cudaErrorInvalidValue;
   const unsigned blocks = (unsigned)((T + tpb - 1) / tpb);
   if (act_dtype == BF_DTYPE_F32) {
@@ -158,25 +261,30 @@ BF_EXPORT int bf_moe_route(const void* h, long long stride, const float* w, int 
     if (smem > 48 * 1024)
       cudaFuncSetAttribute(k, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
     k<<<blocks, MR_WARPS * 32, smem, stream>>>((const float*)h, stride, w, T, width, E, top,
-                                               shared_gate, tpb, route_w, top_ids, top_w);
+                                               shared_gate, tpb, route_w, top_ids, top_w, mode,
+                                               correction, n_groups, keep, identity, route_scale,
+                                               weight_eps);
   } else {
     auto k = moe_route_kernel<__nv_bfloat16>;
     if (smem > 48 * 1024)
       cudaFuncSetAttribute(k, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
     k<<<blocks, MR_WARPS * 32, smem, stream>>>((const __nv_bfloat16*)h, stride, w, T, width, E,
-                                               top, shared_gate, tpb, route_w, top_ids, top_w);
+                                               top, shared_gate, tpb, route_w, top_ids, top_w,
+                                               mode, correction, n_groups, keep, identity,
+                                               route_scale, weight_eps);
   }
   return bf_launch_status();
 }
 
 template <typename A>
 __global__ void moe_act_kernel(const A* __restrict__ gu, const float* __restrict__ route_w,
-                               A* __restrict__ act, int T, int F, int E, int ff, int rw_cols) {
+                               A* __restrict__ act, int T, int F, int E, int ff, int rw_cols,
+                               int shared_gate) {
   const long long i = (long long)blockIdx.x * blockDim.x + threadIdx.x;
   if (i >= (long long)T * F) return;
   const int t = (int)(i / F), c = (int)(i % F);
   const int e = c < E * ff ? c / ff : E;
-  const float wgt = e < rw_cols ? route_w[(size_t)t * rw_cols + e] : 1.f;
+  const float wgt = (e < E || shared_gate) ? route_w[(size_t)t * rw_cols + e] : 1.f;
   float r = 0.f;
   if (wgt != 0.f) {
     const float g = bf_ld(gu + (size_t)t * 2 * F + c), u = bf_ld(gu + (size_t)t * 2 * F + F + c);
@@ -190,13 +298,13 @@ __global__ void moe_act_kernel(const A* __restrict__ gu, const float* __restrict
 __global__ void moe_act_bf16_vec_kernel(const __nv_bfloat16* __restrict__ gu,
                                         const float* __restrict__ route_w,
                                         __nv_bfloat16* __restrict__ act, int T, int F, int E,
-                                        int ff, int rw_cols) {
+                                        int ff, int rw_cols, int shared_gate) {
   const long long i = (long long)blockIdx.x * blockDim.x + threadIdx.x;
   const int F8 = F >> 3;
   if (i >= (long long)T * F8) return;
   const int t = (int)(i / F8), c = (int)(i % F8) << 3;
   const int e = c < E * ff ? c / ff : E;
-  const float wgt = e < rw_cols ? route_w[(size_t)t * rw_cols + e] : 1.f;
+  const float wgt = (e < E || shared_gate) ? route_w[(size_t)t * rw_cols + e] : 1.f;
   uint4 out = make_uint4(0u, 0u, 0u, 0u);
   if (wgt != 0.f) {
     const uint4 g4 = *reinterpret_cast<const uint4*>(gu + (size_t)t * 2 * F + c);
@@ -214,23 +322,55 @@ __global__ void moe_act_bf16_vec_kernel(const __nv_bfloat16* __restrict__ gu,
   *reinterpret_cast<uint4*>(act + (size_t)t * F + c) = out;
 }
 
+// rw_cols: the columns of a row of route_w; shared_gate: column E holds the shared expert's
+// weight (else that expert's weight is one)
 BF_EXPORT int bf_moe_act(const void* gu, const float* route_w, void* act, int T, int F, int E,
-                         int ff, int rw_cols, int act_dtype, cudaStream_t stream) {
+                         int ff, int rw_cols, int shared_gate, int act_dtype,
+                         cudaStream_t stream) {
   if (T <= 0 || F <= 0) return 0;
   const long long n = (long long)T * F;
   const unsigned blocks = (unsigned)((n + 255) / 256);
   if (act_dtype == BF_DTYPE_BF16 && F % 8 == 0 && ff % 8 == 0 &&
       (((uintptr_t)gu | (uintptr_t)act) & 15) == 0) {
     moe_act_bf16_vec_kernel<<<(unsigned)((n / 8 + 255) / 256), 256, 0, stream>>>(
-        (const __nv_bfloat16*)gu, route_w, (__nv_bfloat16*)act, T, F, E, ff, rw_cols);
+        (const __nv_bfloat16*)gu, route_w, (__nv_bfloat16*)act, T, F, E, ff, rw_cols,
+        shared_gate);
     return bf_launch_status();
   }
   if (act_dtype == BF_DTYPE_F32)
     moe_act_kernel<float><<<blocks, 256, 0, stream>>>((const float*)gu, route_w, (float*)act, T,
-                                                      F, E, ff, rw_cols);
+                                                      F, E, ff, rw_cols, shared_gate);
   else
     moe_act_kernel<__nv_bfloat16><<<blocks, 256, 0, stream>>>(
-        (const __nv_bfloat16*)gu, route_w, (__nv_bfloat16*)act, T, F, E, ff, rw_cols);
+        (const __nv_bfloat16*)gu, route_w, (__nv_bfloat16*)act, T, F, E, ff, rw_cols,
+        shared_gate);
+  return bf_launch_status();
+}
+
+// out[t, c] += h[t, c] * route_w[t, col]: the experts that return their input.
+template <typename A>
+__global__ void moe_identity_add_kernel(A* __restrict__ out, const A* __restrict__ h,
+                                        long long stride, const float* __restrict__ route_w,
+                                        int rw_cols, int col, int T, int width) {
+  const long long i = (long long)blockIdx.x * blockDim.x + threadIdx.x;
+  if (i >= (long long)T * width) return;
+  const int t = (int)(i / width), c = (int)(i % width);
+  const float wgt = route_w[(size_t)t * rw_cols + col];
+  if (wgt != 0.f) bf_st(out + i, bf_ld(out + i) + wgt * bf_ld(h + (size_t)t * stride + c));
+}
+
+BF_EXPORT int bf_moe_identity_add(void* out, const void* h, long long stride,
+                                  const float* route_w, int rw_cols, int col, int T, int width,
+                                  int act_dtype, cudaStream_t stream) {
+  if (T <= 0 || width <= 0) return 0;
+  const long long n = (long long)T * width;
+  const unsigned blocks = (unsigned)((n + 255) / 256);
+  if (act_dtype == BF_DTYPE_F32)
+    moe_identity_add_kernel<float><<<blocks, 256, 0, stream>>>(
+        (float*)out, (const float*)h, stride, route_w, rw_cols, col, T, width);
+  else
+    moe_identity_add_kernel<__nv_bfloat16><<<blocks, 256, 0, stream>>>(
+        (__nv_bfloat16*)out, (const __nv_bfloat16*)h, stride, route_w, rw_cols, col, T, width);
   return bf_launch_status();
 }
 
@@ -242,6 +382,10 @@ BF_EXPORT int bf_moe_act(const void* gu, const float* route_w, void* act, int T,
 // moe_sparse_down multiplies them with the expert's columns of the stacked down weight and
 // adds the choices up in that order.  One warp per output row, the token's input in shared
 // memory as float, 16-byte pieces of the rows where the sizes allow.
+//
+// A choice at or beyond E is an expert that returns its input: it has no rows, its activations
+// are zeros, and moe_sparse_down adds the input times the identity column of route_w
+// (`id_col` >= 0) behind the shared expert.
 //
 // act: [T][top * ff + ff_sh] (choice k at k * ff, the shared expert behind them).
 #define MS_WARPS 8
@@ -325,7 +469,7 @@ __global__ void moe_sparse_gate_up_kernel(const A* __restrict__ h, long long str
                                           const int* __restrict__ top_ids,
                                           const float* __restrict__ top_w,
                                           const float* __restrict__ route_w, int rw_cols,
-                                          A* __restrict__ act) {
+                                          int shared_gate, A* __restrict__ act) {
   extern __shared__ __align__(16) float sh[];
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
   const int t = blockIdx.z, k = blockIdx.y;
@@ -336,13 +480,18 @@ __global__ void moe_sparse_gate_up_kernel(const A* __restrict__ h, long long str
   ms_stage<A>(h + (size_t)t * stride, sh, width);
   __syncthreads();
   const int e = shared ? E : top_ids[(size_t)t * top + k];
-  const float wgt = shared ? (E < rw_cols ? route_w[(size_t)t * rw_cols + E] : 1.f)
+  const float wgt = shared ? (shared_gate ? route_w[(size_t)t * rw_cols + E] : 1.f)
                            : top_w[(size_t)t * top + k];
   const size_t base = shared ? (size_t)E * ff : (size_t)e * ff;      // the expert's first row
   const bool vec = (width % 8) == 0 && (((uintptr_t)w_gu) & 15) == 0;
   A* dst = act + (size_t)t * ((size_t)top * ff + ff_sh) + (shared ? (size_t)top * ff : (size_t)k * ff);
   const int rows = min(MS_ROWS, n_rows - row0);
   if (rows <= 0) return;
+  if (!shared && e >= E) {                       // an expert that returns its input: no rows
+    if (lane == 0)
+      for (int r = 0; r < rows; ++r) bf_st(dst + row0 + r, 0.f);
+    return;
+  }
   float g[MS_ROWS], u[MS_ROWS];
   ms_dots<A, MS_ROWS>(w_gu + (base + row0) * width, (size_t)width, rows, sh, width, lane, vec, g);
   ms_dots<A, MS_ROWS>(w_gu + ((size_t)F + base + row0) * width, (size_t)width, rows, sh, width,
@@ -355,7 +504,10 @@ __global__ void moe_sparse_gate_up_kernel(const A* __restrict__ h, long long str
 template <typename A>
 __global__ void moe_sparse_down_kernel(const A* __restrict__ act, const A* __restrict__ w_down,
                                        int width, int F, int E, int ff, int ff_sh, int top,
-                                       const int* __restrict__ top_ids, A* __restrict__ out) {
+                                       const int* __restrict__ top_ids, A* __restrict__ out,
+                                       const A* __restrict__ h, long long h_stride,
+                                       const float* __restrict__ route_w, int rw_cols,
+                                       int id_col) {
   extern __shared__ __align__(16) float sh[];
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
   const int t = blockIdx.y;
@@ -371,6 +523,7 @@ __global__ void moe_sparse_down_kernel(const A* __restrict__ act, const A* __res
 #pragma unroll
   for (int r = 0; r < MS_ROWS; ++r) a[r] = 0.f;
   for (int k = 0; k < top; ++k) {
+    if (top_ids[(size_t)t * top + k] >= E) continue;
     ms_dots<A, MS_ROWS>(wr + (size_t)top_ids[(size_t)t * top + k] * ff, (size_t)F, rows,
                         sh + (size_t)k * ff, ff, lane, vec, part);
 #pragma unroll
@@ -382,14 +535,20 @@ __global__ void moe_sparse_down_kernel(const A* __restrict__ act, const A* __res
 #pragma unroll
     for (int r = 0; r < MS_ROWS; ++r) a[r] += part[r];
   }
-  if (lane == 0)
-    for (int r = 0; r < rows; ++r) bf_st(out + (size_t)t * width + row0 + r, a[r]);
+  if (lane == 0) {
+    const float idw = id_col >= 0 ? route_w[(size_t)t * rw_cols + id_col] : 0.f;
+    for (int r = 0; r < rows; ++r) {
+      if (idw != 0.f) a[r] += idw * bf_ld(h + (size_t)t * h_stride + row0 + r);
+      bf_st(out + (size_t)t * width + row0 + r, a[r]);
+    }
+  }
 }
 
 BF_EXPORT int bf_moe_sparse(const void* h, long long stride, const void* w_gu, const void* w_down,
                             const int* top_ids, const float* top_w, const float* route_w,
                             int rw_cols, void* act, void* out, int T, int width, int E, int ff,
-                            int ff_sh, int top, int act_dtype, cudaStream_t stream) {
+                            int ff_sh, int top, int act_dtype, int shared_gate, int id_col,
+                            cudaStream_t stream) {
   if (T <= 0) return 0;
   const int F = E * ff + ff_sh;
   const int choices = top + (ff_sh ? 1 : 0);
@@ -403,17 +562,17 @@ BF_EXPORT int bf_moe_sparse(const void* h, long long stride, const void* w_gu, c
   if (act_dtype == BF_DTYPE_F32) {
     moe_sparse_gate_up_kernel<float><<<g1, MS_WARPS * 32, (size_t)width * 4, stream>>>(
         (const float*)h, stride, (const float*)w_gu, width, F, E, ff, ff_sh, top, top_ids, top_w,
-        route_w, rw_cols, (float*)act);
+        route_w, rw_cols, shared_gate, (float*)act);
     moe_sparse_down_kernel<float><<<g2, MS_WARPS * 32, (size_t)n_act * 4, stream>>>(
         (const float*)act, (const float*)w_down, width, F, E, ff, ff_sh, top, top_ids,
-        (float*)out);
+        (float*)out, (const float*)h, stride, route_w, rw_cols, id_col);
   } else {
     moe_sparse_gate_up_kernel<__nv_bfloat16><<<g1, MS_WARPS * 32, (size_t)width * 4, stream>>>(
         (const __nv_bfloat16*)h, stride, (const __nv_bfloat16*)w_gu, width, F, E, ff, ff_sh, top,
-        top_ids, top_w, route_w, rw_cols, (__nv_bfloat16*)act);
+        top_ids, top_w, route_w, rw_cols, shared_gate, (__nv_bfloat16*)act);
     moe_sparse_down_kernel<__nv_bfloat16><<<g2, MS_WARPS * 32, (size_t)n_act * 4, stream>>>(
         (const __nv_bfloat16*)act, (const __nv_bfloat16*)w_down, width, F, E, ff, ff_sh, top,
-        top_ids, (__nv_bfloat16*)out);
+        top_ids, (__nv_bfloat16*)out, (const __nv_bfloat16*)h, stride, route_w, rw_cols, id_col);
   }
   return bf_launch_status();
 }

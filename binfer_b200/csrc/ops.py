@@ -238,7 +238,8 @@ def paged_attention_generic(q: torch.Tensor, k_cache: torch.Tensor, v_cache: tor
                             slopes: Optional[torch.Tensor] = None,
                             sinks: Optional[torch.Tensor] = None, value_dim: Optional[int] = None,
                             keep_first: int = 0, out_scale: float = 1.0,
-                            v_stride: int = 0) -> None:
+                            v_stride: int = 0, log_slope: Optional[torch.Tensor] = None,
+                            log_rate: Optional[torch.Tensor] = None) -> None:
     """Attention of every token row over its request's pages, any sizes.  ``softcap``,
     ``slopes`` (float32 ``[nh]``) and ``sinks`` (float32 ``[nh]``) change the scores as
     ``config.specs.ScoreSpec`` says; by default nothing is changed.  ``value_dim``: size of a
@@ -247,15 +248,20 @@ def paged_attention_generic(q: torch.Tensor, k_cache: torch.Tensor, v_cache: tor
     wider buffers (rows ``nh * d`` and ``nh * value_dim`` long); ``out_scale`` multiplies the
     result.  ``v_stride``: elements between the value rows of neighbouring tokens of a page
     (0: ``value_dim``); with ``v_cache = k_cache`` and ``v_stride = d`` a token's value is the
-    first ``value_dim`` numbers of its key."""
+    first ``value_dim`` numbers of its key.  ``log_slope`` and ``log_rate`` (float32 ``[nh]``
+    each, together or not at all): ``log_slope_h ln(1 + log_rate_h (p - j))`` is taken off the
+    score of the query at p and the key at j."""
     T = q.shape[0]
     dv = d if value_dim is None else int(value_dim)
+    if (log_slope is None) != (log_rate is None):
+        raise KernelError("attention: log_slope and log_rate go together")
     if d > GENERIC_MAX_HEAD_DIM or dv > GENERIC_MAX_VALUE_DIM:
         raise KernelError(f"attention: head sizes {d}, {dv} are not supported (at most "
                           f"{GENERIC_MAX_HEAD_DIM}, {GENERIC_MAX_VALUE_DIM})")
     if q.stride(1) != 1 or out.stride(1) != 1:
         raise KernelError("attention: rows of q and out must be contiguous")
-    for name, t in (("slopes", slopes), ("sinks", sinks)):
+    for name, t in (("slopes", slopes), ("sinks", sinks), ("log_slope", log_slope),
+                    ("log_rate", log_rate)):
         if t is not None:
             _want(t, torch.float32, name)
             if t.numel() != nh:
@@ -266,7 +272,8 @@ def paged_attention_generic(q: torch.Tensor, k_cache: torch.Tensor, v_cache: tor
         _c_int(nkv), _c_int(d), _c_int(k_cache.shape[2]), _c_int(k_cache.shape[0]),
         _c_int(window or 0), _c_float(scale), _c_float(softcap), _ptr(slopes), _ptr(sinks),
         _c_int(_dtype_code(q)), _ptr(err), _c_int(dv), _c_int(keep_first), _c_ll(q.stride(0)),
-        _c_ll(out.stride(0)), _c_float(out_scale), _c_ll(v_stride), _stream())
+        _c_ll(out.stride(0)), _c_float(out_scale), _c_ll(v_stride), _ptr(log_slope),
+        _ptr(log_rate), _stream())
 
 
 GENERIC_MAX_HEAD_DIM, GENERIC_MAX_VALUE_DIM = 1024, 512
@@ -509,7 +516,9 @@ def conv_encode(proj: torch.Tensor, conv_w: Optional[torch.Tensor], taps: int,
                 k_cache: Optional[torch.Tensor], v_cache: Optional[torch.Tensor], nh: int,
                 nkv: int, dk: int, dv: int, unit_norm: bool, eps: float,
                 err: torch.Tensor, pre_factor: Optional[torch.Tensor] = None,
-                pre_weight: Optional[torch.Tensor] = None, rot_magnitude: float = 1.0) -> None:
+                pre_weight: Optional[torch.Tensor] = None, rot_magnitude: float = 1.0,
+                head_weight: Optional[torch.Tensor] = None,
+                q_head_scale: Optional[torch.Tensor] = None) -> None:
     """``proj`` rows hold ``[q: nh dk | k: nkv dk | v: nkv dv]`` (a column block of a wider
     buffer is fine).  Per channel a causal convolution over the request's tokens with
     ``conv_w`` float32 ``[channels, taps]`` (``taps`` 0: none), whose reach behind the
@@ -520,8 +529,18 @@ def conv_encode(proj: torch.Tensor, conv_w: Optional[torch.Tensor], taps: int,
     ``pre_factor`` float32 ``[T, 2]`` and ``pre_weight`` float32 ``[(nh + nkv) dk]``: q and k are
     multiplied by their token's factor and their channel's weight before the rotation (a norm
     over a whole projection: :func:`section_rms` takes the factors).  ``rot_magnitude``
-    multiplies cosines and sines."""
+    multiplies cosines and sines.  ``head_weight`` float32 ``[2, dk]``: behind the heads' norm,
+    every q head is multiplied by the first row and every k head by the second.
+    ``q_head_scale`` float32 ``[nh]``: q head h is multiplied by its number."""
     T = proj.shape[0]
+    if head_weight is not None:
+        _want(head_weight, torch.float32, "head_weight")
+        if tuple(head_weight.shape) != (2, dk) or not head_weight.is_contiguous():
+            raise KernelError("conv_encode: head_weight must be contiguous [2, dk]")
+    if q_head_scale is not None:
+        _want(q_head_scale, torch.float32, "q_head_scale")
+        if q_head_scale.numel() != nh:
+            raise KernelError("conv_encode: q_head_scale must have one number per query head")
     if pre_factor is not None:
         _want(pre_factor, torch.float32, "pre_factor"); _want(pre_weight, torch.float32, "pre_weight")
         if tuple(pre_factor.shape) != (T, 2) or pre_weight.numel() != (nh + nkv) * dk:
@@ -557,7 +576,8 @@ def conv_encode(proj: torch.Tensor, conv_w: Optional[torch.Tensor], taps: int,
          _ptr(slots), _ptr(q_out), _c_ll(q_out.stride(0)), _ptr(k_cache), _ptr(v_cache), _c_int(T),
          _c_int(nh), _c_int(nkv), _c_int(dk), _c_int(dv), _c_int(page_size), _c_ll(num_slots),
          _c_int(1 if unit_norm else 0), _c_float(eps), _c_int(_dtype_code(proj)), _ptr(table),
-         _ptr(err), _ptr(pre_factor), _ptr(pre_weight), _c_float(rot_magnitude), _stream())
+         _ptr(err), _ptr(pre_factor), _ptr(pre_weight), _c_float(rot_magnitude),
+         _ptr(head_weight), _ptr(q_head_scale), _stream())
 
 
 def conv_state_shift(proj: torch.Tensor, state: torch.Tensor, state_slots: torch.Tensor,
@@ -616,6 +636,106 @@ def retention_scan(proj: torch.Tensor, q_off: int, k_off: int, v_off: int, decay
     _launches += 1          # two kernels: the rotation and the scan
 
 
+def linear_scan(qk: torch.Tensor, vf: torch.Tensor, tok_decay: torch.Tensor, state: torch.Tensor,
+                q_start: torch.Tensor, state_slots: torch.Tensor, o_raw: torch.Tensor, B: int,
+                heads: int, qk_heads: int, dk: int, dv: int, err: torch.Tensor,
+                max_q: int = 0) -> None:
+    """The recurrence ``S <- decay[t, h] S + k v^T, o = S^T q`` over every request's tokens of
+    the step, on inputs that are float already: ``qk [T, 2, qk_heads, dk]`` (q, then k; head h
+    reads head ``h // (heads / qk_heads)``), ``vf [T, heads, dv]``, ``tok_decay [T, heads]``.
+    ``state`` float32 ``[slots, heads * dv * dk]`` (a column block of the slots' storage);
+    ``o_raw`` float32 ``[T, heads dv]``.  ``max_q``: the most tokens one request brings."""
+    for name, t in (("qk", qk), ("vf", vf), ("tok_decay", tok_decay), ("o_raw", o_raw)):
+        _want(t, torch.float32, name)
+        if not t.is_contiguous():
+            raise KernelError(f"linear_scan: {name} must be contiguous")
+    T = vf.shape[0]
+    if (dk > RETENTION_MAX_QK_DIM or qk_heads <= 0 or heads % qk_heads
+            or qk.numel() != T * 2 * qk_heads * dk or vf.numel() != T * heads * dv
+            or tok_decay.numel() != T * heads or o_raw.numel() != T * heads * dv):
+        raise KernelError(f"linear_scan: qk [T, 2, qk_heads, dk], vf [T, heads, dv], tok_decay "
+                          f"[T, heads], keys of at most {RETENTION_MAX_QK_DIM}")
+    if (state.dtype != torch.float32 or state.stride(1) != 1
+            or state.shape[1] != heads * dk * dv):
+        raise KernelError("linear_scan: state must be float32 [slots, heads * dk * dv]")
+    _run("linear_scan", lib().bf_linear_scan, _ptr(qk), _ptr(vf), _ptr(tok_decay), _ptr(state),
+         _c_ll(state.stride(0)), _ptr(q_start), _ptr(state_slots), _c_int(state.shape[0]),
+         _ptr(o_raw), _c_int(T), _c_int(B), _c_int(max_q if max_q > 0 else T), _c_int(heads),
+         _c_int(qk_heads), _c_int(dk), _c_int(dv), _ptr(err), _stream())
+
+
+def mamba2_encode(proj: torch.Tensor, xbc_off: int, dt_off: int, conv_w: Optional[torch.Tensor],
+                  conv_b: Optional[torch.Tensor], taps: int, state: Optional[torch.Tensor],
+                  state_slots: torch.Tensor, seq_of_token: torch.Tensor, q_start: torch.Tensor,
+                  A_log: torch.Tensor, dt_bias: torch.Tensor, D: torch.Tensor, qk: torch.Tensor,
+                  vf: torch.Tensor, skip: torch.Tensor, decay: torch.Tensor, heads: int,
+                  groups: int, N: int, P: int, err: torch.Tensor) -> None:
+    """What lies between a state space layer's input projection and its recurrence.  ``proj``
+    rows hold, from ``xbc_off``, ``[x: heads P | B: groups N | C: groups N]`` (the channels that
+    pass the causal convolution ``conv_w`` float32 ``[channels, taps]`` with the bias ``conv_b``
+    and ``silu``; the reach behind the step's first row is read from ``state`` float32
+    ``[slots, (taps-1) * channels]``, which is not changed: :func:`conv_state_shift`) and, from
+    ``dt_off``, one step size per head.  Results, float32: ``qk [T, 2, groups, N]`` (C, then
+    B), ``vf [T, heads, P]`` (``dt x``), ``skip [T, heads, P]`` (``D_h x``), ``decay [T, heads]``
+    (``exp(-exp(A_log_h) dt)``) with ``dt = softplus(dt + dt_bias_h)``."""
+    T = proj.shape[0]
+    C = heads * P + 2 * groups * N
+    if proj.stride(1) != 1 or xbc_off + C > proj.shape[1] or dt_off + heads > proj.shape[1]:
+        raise KernelError("mamba2_encode: proj rows must be contiguous and hold the channels")
+    if taps > CONV_MAX_TAPS:
+        raise KernelError(f"mamba2_encode: at most {CONV_MAX_TAPS} taps")
+    if taps >= 1:
+        _want(conv_w, torch.float32, "conv_w")
+        if tuple(conv_w.shape) != (C, taps) or not conv_w.is_contiguous():
+            raise KernelError("mamba2_encode: conv_w must be [channels, taps]")
+    if conv_b is not None:
+        _want(conv_b, torch.float32, "conv_b")
+        if conv_b.numel() != C:
+            raise KernelError("mamba2_encode: conv_b must be [channels]")
+    if taps > 1 and (state.dtype != torch.float32 or state.stride(1) != 1
+                     or state.shape[1] != (taps - 1) * C):
+        raise KernelError("mamba2_encode: state must be float32 [slots, (taps-1) * channels]")
+    for name, t, n in (("A_log", A_log, heads), ("dt_bias", dt_bias, heads), ("D", D, heads),
+                       ("qk", qk, T * 2 * groups * N), ("vf", vf, T * heads * P),
+                       ("skip", skip, T * heads * P), ("decay", decay, T * heads)):
+        _want(t, torch.float32, name)
+        if t.numel() != n or not t.is_contiguous():
+            raise KernelError(f"mamba2_encode: {name} has the wrong size")
+    _run("mamba2_encode", lib().bf_mamba2_encode, _ptr(proj), _c_ll(proj.stride(0)),
+         _c_ll(xbc_off), _c_ll(dt_off), _ptr(conv_w if taps >= 1 else None), _ptr(conv_b),
+         _c_int(taps), _ptr(state), _c_ll(state.stride(0) if state is not None else 0),
+         _ptr(state_slots), _c_int(state.shape[0] if state is not None else 0),
+         _ptr(seq_of_token), _ptr(q_start), _ptr(A_log), _ptr(dt_bias), _ptr(D), _ptr(qk),
+         _ptr(vf), _ptr(skip), _ptr(decay), _c_int(T), _c_int(heads), _c_int(groups), _c_int(N),
+         _c_int(P), _c_int(_dtype_code(proj)), _ptr(err), _stream())
+
+
+def gate_norm_out(o_raw: torch.Tensor, skip: Optional[torch.Tensor], proj: torch.Tensor,
+                  z_off: int, weight: Optional[torch.Tensor], out: torch.Tensor, parts: int,
+                  eps: float) -> None:
+    """``y = (o_raw + skip) * silu(proj[:, z_off:])``, then an RMS norm in ``parts`` equal parts
+    of the row (each by its own root mean square), times ``weight`` float32 ``[n]``; the gate
+    comes before the norm.  ``o_raw`` and ``skip`` float32 ``[T, n]``; ``out [T, n]`` of the
+    projection's type (a column block of a wider buffer is fine)."""
+    _want(o_raw, torch.float32, "o_raw")
+    T, n = o_raw.shape
+    if skip is not None:
+        _want(skip, torch.float32, "skip")
+        if skip.numel() != T * n or not skip.is_contiguous():
+            raise KernelError("gate_norm_out: skip must be contiguous [T, n]")
+    if weight is not None:
+        _want(weight, torch.float32, "weight")
+        if weight.numel() != n:
+            raise KernelError("gate_norm_out: weight must have n numbers")
+    if (not o_raw.is_contiguous() or out.stride(1) != 1 or out.dtype != proj.dtype
+            or proj.stride(1) != 1 or parts <= 0 or n % parts or z_off + n > proj.shape[1]):
+        raise KernelError("gate_norm_out: contiguous rows, out of the projection's type, parts "
+                          "that divide the row")
+    _run("gate_norm_out", lib().bf_gate_norm_out, _ptr(o_raw), _ptr(skip), _ptr(proj),
+         _c_ll(proj.stride(0)), _c_ll(z_off), _ptr(weight), _ptr(out), _c_ll(out.stride(0)),
+         _c_int(T), _c_int(n), _c_int(parts), _c_float(eps), _c_int(_dtype_code(proj)), _stream())
+
+
 def retention_out(o_raw: torch.Tensor, proj: torch.Tensor, g_off: int, out: torch.Tensor,
                   heads: int, dv: int, eps: float, out_scale: float = 1.0) -> None:
     """``out = o_raw / rms_per_head(o_raw) * silu(proj[:, g_off:]) * out_scale``; ``out`` may be
@@ -643,13 +763,28 @@ def section_rms(x: torch.Tensor, off0: int, n0: int, off1: int, n1: int, eps: fl
          _c_int(_dtype_code(x)), _stream())
 
 
+def section_norm(x: torch.Tensor, off: int, n: int, weight: torch.Tensor, eps: float,
+                 out: torch.Tensor) -> None:
+    """``out[t] = rmsnorm(x[t, off:off + n]) * weight``: an RMS norm with a weight (float32
+    ``[n]``) over a column section of every row, into ``out [T, n]`` of ``x``'s type."""
+    _want(weight, torch.float32, "weight")
+    T = x.shape[0]
+    if (x.stride(1) != 1 or out.stride(1) != 1 or out.dtype != x.dtype or weight.numel() != n
+            or tuple(out.shape) != (T, n) or off < 0 or off + n > x.shape[1]):
+        raise KernelError("section_norm: contiguous rows, weight [n], out [T, n] of x's type")
+    _run("section_norm", lib().bf_section_norm, _ptr(x), _c_ll(x.stride(0)), _c_ll(off), _c_int(n),
+         _ptr(weight), _c_float(eps), _ptr(out), _c_ll(out.stride(0)), _c_int(T),
+         _c_int(_dtype_code(x)), _stream())
+
+
 def latent_encode(proj: torch.Tensor, q_off: int, kv_off: int, norm_w: torch.Tensor, eps: float,
                   inv_freq: Optional[torch.Tensor], interleaved: bool, rot_magnitude: float,
                   positions: torch.Tensor, slots: Optional[torch.Tensor], q_abs: torch.Tensor,
                   cache: Optional[torch.Tensor], heads: int, d: int, dr: int, rank: int,
-                  err: torch.Tensor) -> None:
+                  err: torch.Tensor, q: Optional[torch.Tensor] = None) -> None:
     """Attention over a cached latent, before the scores: ``proj`` rows hold ``heads`` query
-    heads of ``[d plain | dr rotated]`` from ``q_off`` and ``[rank | dr]`` from ``kv_off``.
+    heads of ``[d plain | dr rotated]`` from ``q_off`` (or ``q [T, heads (d + dr)]`` holds
+    them, a buffer of its own of ``proj``'s type) and ``[rank | dr]`` from ``kv_off``.
     The cache row of a token (pages ``[pages, 1, page_size, rank + dr]``, at ``slots``)
     becomes ``[rmsnorm(first rank) * norm_w | rotated dr]``; ``q_abs [T, heads, rank + dr]``
     gets every head's rotated part at ``[rank, rank + dr)`` and is otherwise left alone."""
@@ -659,14 +794,18 @@ def latent_encode(proj: torch.Tensor, q_off: int, kv_off: int, norm_w: torch.Ten
         raise KernelError("latent_encode: contiguous rows, q_abs contiguous and of proj's type")
     if tuple(q_abs.shape) != (T, heads, rank + dr) or norm_w.numel() != rank:
         raise KernelError("latent_encode: q_abs must be [T, heads, rank + dr], norm_w [rank]")
+    if q is None:
+        q = proj[:, q_off:q_off + heads * (d + dr)]
+    if q.dtype != proj.dtype or q.stride(1) != 1 or tuple(q.shape) != (T, heads * (d + dr)):
+        raise KernelError("latent_encode: q must be [T, heads (d + dr)] of proj's type")
     rot_half = 0 if inv_freq is None else inv_freq.numel()
     page_size, num_slots = 1, 0
     if cache is not None:
         if not cache.is_contiguous() or cache.shape[1] != 1 or cache.shape[3] != rank + dr:
             raise KernelError("latent_encode: pages must be contiguous [pages, 1, size, rank + dr]")
         page_size, num_slots = cache.shape[2], cache.shape[0] * cache.shape[2]
-    _run("latent_encode", lib().bf_latent_encode, _ptr(proj), _c_ll(proj.stride(0)), _c_ll(q_off),
-         _c_ll(kv_off), _ptr(norm_w), _c_float(eps), _ptr(inv_freq), _c_int(rot_half),
+    _run("latent_encode", lib().bf_latent_encode, _ptr(proj), _c_ll(proj.stride(0)), _ptr(q),
+         _c_ll(q.stride(0)), _c_ll(kv_off), _ptr(norm_w), _c_float(eps), _ptr(inv_freq), _c_int(rot_half),
          _c_int(1 if interleaved else 0), _c_float(rot_magnitude), _ptr(positions),
          _ptr(slots if cache is not None else None), _ptr(q_abs), _ptr(cache), _c_int(T),
          _c_int(heads), _c_int(d), _c_int(dr), _c_int(rank), _c_int(page_size), _c_ll(num_slots),
@@ -797,36 +936,82 @@ def stream_inject(resid: torch.Tensor, delta: Optional[torch.Tensor],
 
 # ---------------------------------------------------------------- mixture of experts
 def moe_route(h: torch.Tensor, w: torch.Tensor, experts: int, top: int, shared_gate: bool,
-              route_w: torch.Tensor, top_ids: torch.Tensor, top_w: torch.Tensor) -> None:
-    """Router of a mixture of experts: ``w`` float32 ``[experts (+1), width]`` (the last row the
-    shared expert's gate when ``shared_gate``), ``h [T, width]``.  ``route_w`` float32
-    ``[T, experts (+1)]`` gets every expert's weight for the token (zero: not chosen; the
-    last column ``sigmoid(w_sg . h)``), ``top_ids`` int32 and ``top_w`` float32 ``[T, top]``
-    the chosen experts, largest logit first."""
+              route_w: torch.Tensor, top_ids: torch.Tensor, top_w: torch.Tensor,
+              scoring: str = "softmax_top", correction: Optional[torch.Tensor] = None,
+              groups: int = 1, groups_keep: int = 1, identity: int = 0,
+              route_scale: float = 1.0, weight_eps: float = 0.0) -> None:
+    """Router of a mixture of experts: ``w`` float32 ``[experts + identity (+1), width]`` (the
+    last row the shared expert's gate when ``shared_gate``), ``h [T, width]``.  ``route_w``
+    float32 ``[T, experts (+1) (+1)]`` gets every expert's weight for the token (zero: not
+    chosen), then ``sigmoid(w_sg . h)`` when ``shared_gate``, then (``identity`` > 0) the sum of
+    the weights of the chosen outputs that stand for experts returning their input;
+    ``top_ids`` int32 and ``top_w`` float32 ``[T, top]`` the chosen outputs, best first.
+
+    ``scoring`` "softmax_top": the largest logits are chosen and weighted by the softmax over
+    them alone.  "softmax_all": scores are the softmax over all ``experts + identity``
+    outputs, ``correction`` (float32, one number per output) is added for the choice only,
+    with ``groups`` > 1 only the outputs of the ``groups_keep`` groups with the largest best
+    choice score can be chosen, and the weights are the chosen scores over their sum (plus
+    ``weight_eps``) times ``route_scale``."""
     T, width = h.shape
-    rows = experts + (1 if shared_gate else 0)
+    if scoring not in ("softmax_top", "softmax_all"):
+        raise KernelError(f"moe_route: unknown scoring {scoring!r}")
+    mode = 1 if scoring == "softmax_all" else 0
+    if mode == 0 and (identity or groups > 1 or correction is not None):
+        raise KernelError("moe_route: corrections, groups and identity outputs go with the "
+                          "softmax over all outputs")
+    rows = experts + identity + (1 if shared_gate else 0)
+    cols = experts + (1 if shared_gate else 0) + (1 if identity else 0)
     _want(w, torch.float32, "w"); _want(route_w, torch.float32, "route_w")
     _want(top_ids, torch.int32, "top_ids"); _want(top_w, torch.float32, "top_w")
-    if tuple(w.shape) != (rows, width) or tuple(route_w.shape) != (T, rows) or h.stride(1) != 1:
-        raise KernelError("moe_route: w must be [experts (+1), width], route_w [T, experts (+1)]")
+    if (tuple(w.shape) != (rows, width) or tuple(route_w.shape) != (T, cols) or h.stride(1) != 1
+            or not route_w.is_contiguous()):
+        raise KernelError("moe_route: w must be [experts + identity (+1), width], route_w "
+                          "[T, experts (+1) (+1)]")
+    if correction is not None:
+        _want(correction, torch.float32, "correction")
+        if correction.numel() != experts + identity:
+            raise KernelError("moe_route: correction must have one number per router output")
+    n = experts + identity
+    if (groups < 1 or n % groups or not 1 <= groups_keep <= groups or not 1 <= top <= n
+            or top > groups_keep * (n // groups)):
+        raise KernelError("moe_route: groups must divide the outputs and hold the choices")
     _run("moe_route", lib().bf_moe_route, _ptr(h), _c_ll(h.stride(0)), _ptr(w), _c_int(T),
          _c_int(width), _c_int(experts), _c_int(top), _c_int(1 if shared_gate else 0),
-         _ptr(route_w), _ptr(top_ids), _ptr(top_w), _c_int(_dtype_code(h)), _stream())
+         _ptr(route_w), _ptr(top_ids), _ptr(top_w), _c_int(_dtype_code(h)), _c_int(mode),
+         _ptr(correction), _c_int(groups), _c_int(groups_keep), _c_int(identity),
+         _c_float(route_scale), _c_float(weight_eps), _stream())
 
 
 def moe_act(gu: torch.Tensor, route_w: torch.Tensor, act: torch.Tensor, experts: int,
-            ff: int) -> None:
+            ff: int, shared_gate: Optional[bool] = None) -> None:
     """``act[t, c] = silu(gu[t, c]) * gu[t, F + c] * route_w[t, expert(c)]`` with
-    ``expert(c) = c // ff`` for ``c < experts * ff`` and the column behind the experts' for the
-    rest (weight one if ``route_w`` has no such column)."""
+    ``expert(c) = c // ff`` for ``c < experts * ff``; the columns behind the experts' (a shared
+    expert) take column ``experts`` of ``route_w`` when ``shared_gate``, else the weight one
+    (None: when ``route_w`` has exactly one column more than there are experts)."""
     T, F = act.shape
     _want(route_w, torch.float32, "route_w")
     if tuple(gu.shape) != (T, 2 * F) or not gu.is_contiguous() or not act.is_contiguous() \
-            or gu.dtype != act.dtype or route_w.shape[0] != T:
+            or gu.dtype != act.dtype or route_w.shape[0] != T or not route_w.is_contiguous():
         raise KernelError("moe_act: gu must be contiguous [T, 2 F] of act's type")
+    if shared_gate is None:
+        shared_gate = route_w.shape[1] == experts + 1
     _run("moe_act", lib().bf_moe_act, _ptr(gu), _ptr(route_w), _ptr(act), _c_int(T), _c_int(F),
-         _c_int(experts), _c_int(ff), _c_int(route_w.shape[1]), _c_int(_dtype_code(act)),
-         _stream())
+         _c_int(experts), _c_int(ff), _c_int(route_w.shape[1]), _c_int(1 if shared_gate else 0),
+         _c_int(_dtype_code(act)), _stream())
+
+
+def moe_identity_add(out: torch.Tensor, h: torch.Tensor, route_w: torch.Tensor, col: int) -> None:
+    """``out[t] += h[t] * route_w[t, col]``: the experts that return their input."""
+    _want(route_w, torch.float32, "route_w")
+    T, width = out.shape
+    if (not out.is_contiguous() or h.stride(1) != 1 or h.dtype != out.dtype
+            or tuple(h.shape) != (T, width) or route_w.shape[0] != T
+            or not route_w.is_contiguous() or not 0 <= col < route_w.shape[1]):
+        raise KernelError("moe_identity_add: out contiguous [T, width], h of its shape and type")
+    _run("moe_identity_add", lib().bf_moe_identity_add, _ptr(out), _ptr(h), _c_ll(h.stride(0)),
+         _ptr(route_w), _c_int(route_w.shape[1]), _c_int(col), _c_int(T), _c_int(width),
+         _c_int(_dtype_code(out)), _stream())
 
 
 def moe_sparse_takes(width: int, ff: int, ff_sh: int, top: int) -> bool:
@@ -837,13 +1022,19 @@ def moe_sparse_takes(width: int, ff: int, ff_sh: int, top: int) -> bool:
 
 def moe_sparse(h: torch.Tensor, w_gate_up: torch.Tensor, w_down: torch.Tensor,
                top_ids: torch.Tensor, top_w: torch.Tensor, route_w: torch.Tensor,
-               out: torch.Tensor, experts: int, ff: int, ff_sh: int, top: int) -> None:
+               out: torch.Tensor, experts: int, ff: int, ff_sh: int, top: int,
+               shared_gate: Optional[bool] = None, identity_col: int = -1) -> None:
     """The mixture's output for a step of very few tokens, reading only the experts that
     were chosen (and the shared one): ``w_gate_up [2 F, width]`` and ``w_down [width, F]`` are
     the stacked weights (``F = experts * ff + ff_sh``), ``top_ids``/``top_w``/``route_w`` what
-    :func:`moe_route` left; ``out [T, width]``."""
+    :func:`moe_route` left; ``out [T, width]``.  ``shared_gate``: column ``experts`` of
+    ``route_w`` is the shared expert's weight (None: when ``route_w`` has exactly one column
+    more than there are experts).  ``identity_col`` >= 0: chosen ids from ``experts`` on return
+    their input, and that column of ``route_w`` holds their weights' sum."""
     T, width = h.shape
     F = experts * ff + ff_sh
+    if shared_gate is None:
+        shared_gate = route_w.shape[1] == experts + 1
     if (tuple(w_gate_up.shape) != (2 * F, width) or tuple(w_down.shape) != (width, F)
             or not w_gate_up.is_contiguous() or not w_down.is_contiguous()
             or w_gate_up.dtype != h.dtype or w_down.dtype != h.dtype or h.stride(1) != 1
@@ -857,7 +1048,8 @@ def moe_sparse(h: torch.Tensor, w_gate_up: torch.Tensor, w_down: torch.Tensor,
     _run("moe_sparse", lib().bf_moe_sparse, _ptr(h), _c_ll(h.stride(0)), _ptr(w_gate_up),
          _ptr(w_down), _ptr(top_ids), _ptr(top_w), _ptr(route_w), _c_int(route_w.shape[1]),
          _ptr(act), _ptr(out), _c_int(T), _c_int(width), _c_int(experts), _c_int(ff),
-         _c_int(ff_sh), _c_int(top), _c_int(_dtype_code(h)), _stream())
+         _c_int(ff_sh), _c_int(top), _c_int(_dtype_code(h)), _c_int(1 if shared_gate else 0),
+         _c_int(identity_col), _stream())
     global _launches
     _launches += 1          # two kernels
 

@@ -10,6 +10,12 @@
 //
 // With `act` 1, q, k and v pass silu first (lightning attention).
 //
+// The scan also runs recurrences whose decay differs from token to token and whose q and k
+// are shared by several heads (a state space layer in its scalar-decay form: q = C, k = B,
+// v = dt x): bf_linear_scan takes q, k and v in float as the encode kernel would leave them,
+// q and k with `qk_heads` heads (head h reads head h / (H / qk_heads)), and a decay per
+// (token, head), which travels through shared memory beside v.
+//
 // retention_encode: q and k of every (token, head), turned and scaled, as float rows
 // `qk [T][2][H][dk]`, and the head's v in float `vf [T][H][dv]` (one warp per (token, head);
 // the scan's blocks, several per head, read them from there by asynchronous copies instead
@@ -97,18 +103,21 @@ __device__ __forceinline__ void ret_cp4(float* smem, const float* gmem) {
 
 // KST: the lanes per column where they are known when the kernel is compiled (the rounds of
 // shuffles then unroll), 0: `ks_rt` of them.
-template <int R, int CV, int KST>
+// TD: the decay comes per (token, head) from `tok_decay [T][H]` instead of per head from `decays`.
+template <int R, int CV, int KST, bool TD>
 __global__ void __launch_bounds__(RET_THREADS) retention_scan_kernel(
     const float* __restrict__ vf, const float* __restrict__ qk, const float* __restrict__ decays,
     float* __restrict__ state, long long state_stride, const int* __restrict__ q_start,
     const int* __restrict__ state_slots, int n_slots, float* __restrict__ o_raw, int H, int dk,
-    int dv, int ks_rt, int stage, int* __restrict__ err) {
+    int dv, int ks_rt, int stage, int* __restrict__ err, const float* __restrict__ tok_decay,
+    int QH) {
   extern __shared__ __align__(16) float sh[];
   const int KS = KST ? KST : ks_rt;
   const int cols = RET_THREADS / KS * CV;
   const int dkp = KS * R;                   // dk rounded up to what the lanes of a column hold
-  // two buffers of [stage][dkp] q, [stage][dkp] k, [stage][cols] v
+  // two buffers of [stage][dkp] q, [stage][dkp] k, [stage][cols] v (TD: and [stage] decays)
   const int b = blockIdx.z, h = blockIdx.y, col0 = blockIdx.x * cols;
+  const int hq = h / (H / QH);              // the head of q and k that this head reads
   const int tid = threadIdx.x;
   const int cg = tid / KS, part = tid % KS;
   const int col = col0 + cg * CV;           // the lane's first column
@@ -119,7 +128,7 @@ __global__ void __launch_bounds__(RET_THREADS) retention_scan_kernel(
     if (tid == 0) atomicOr(err, BF_ERR_SLOT);
     return;
   }
-  const float decay = decays[h];
+  const float decay_h = TD ? 1.f : decays[h];
   float* sp = state + (size_t)slot * state_stride + (size_t)h * dv * dk + (size_t)part * R;
   float S[CV][R];
   // whole rows of four floats where the sizes and the slot's address allow it
@@ -143,7 +152,7 @@ __global__ void __launch_bounds__(RET_THREADS) retention_scan_kernel(
 
   // A stage on its way into buffer `buf`: q and k rows by asynchronous 16-byte copies where
   // the rows allow it, v (in float since the first kernel) by asynchronous copies of one.
-  const int buf_elems = stage * (2 * dkp + cols);
+  const int buf_elems = stage * (2 * dkp + cols) + (TD ? stage : 0);
   const bool rows16 = (dk & 3) == 0 && dkp == dk;
   auto issue = [&](int s0, int buf) {
     const int sn = min(stage, n - s0);
@@ -158,18 +167,18 @@ __global__ void __launch_bounds__(RET_THREADS) retention_scan_kernel(
       for (int idx = tid; idx < sn * d4; idx += RET_THREADS) {
         const int c = idx / d4, i = idx - c * d4;
         const int at = c * d4 + (i % (R / 4)) * KS + i / (R / 4);
-        const float* row = qk + ((size_t)(t0 + s0 + c) * 2 * H + h) * dk + 4 * i;
+        const float* row = qk + ((size_t)(t0 + s0 + c) * 2 * QH + hq) * dk + 4 * i;
         ret_cp16(qd + 4 * at, row);
-        ret_cp16(kd + 4 * at, row + (size_t)H * dk);
+        ret_cp16(kd + 4 * at, row + (size_t)QH * dk);
       }
     } else {
       for (int idx = tid; idx < sn * dkp; idx += RET_THREADS) {
         const int c = idx / dkp, i = idx % dkp;
         const int pt = i / R, r = i % R;
         const int at = c * dkp + ((r >> 2) * KS + pt) * 4 + (r & 3);
-        const float* row = qk + ((size_t)(t0 + s0 + c) * 2 * H + h) * dk;
+        const float* row = qk + ((size_t)(t0 + s0 + c) * 2 * QH + hq) * dk;
         qd[at] = i < dk ? row[i] : 0.f;
-        kd[at] = i < dk ? row[(size_t)H * dk + i] : 0.f;
+        kd[at] = i < dk ? row[(size_t)QH * dk + i] : 0.f;
       }
     }
     for (int idx = tid; idx < sn * cols; idx += RET_THREADS) {
@@ -178,6 +187,11 @@ __global__ void __launch_bounds__(RET_THREADS) retention_scan_kernel(
         ret_cp4(vd + idx, vf + ((size_t)(t0 + s0 + c) * H + h) * dv + col0 + j);
       else
         vd[idx] = 0.f;
+    }
+    if (TD) {
+      float* dd = vd + stage * cols;
+      for (int c = tid; c < sn; c += RET_THREADS)
+        ret_cp4(dd + c, tok_decay + (size_t)(t0 + s0 + c) * H + h);
     }
     asm volatile("cp.async.commit_group;" ::);
   };
@@ -195,6 +209,7 @@ __global__ void __launch_bounds__(RET_THREADS) retention_scan_kernel(
     const float* qs = sh + (size_t)buf * buf_elems;
     const float* ks_ = qs + stage * dkp;
     const float* vs = ks_ + stage * dkp;
+    const float* ds = vs + stage * cols;
     for (int c0 = 0; c0 < sn; c0 += RET_CHUNK) {
       const int cn = min(RET_CHUNK, sn - c0);
       float acc[RET_CHUNK][CV];
@@ -204,8 +219,10 @@ __global__ void __launch_bounds__(RET_THREADS) retention_scan_kernel(
       // before; the state's own chain is one multiply-add a token (k v is formed beside it).
       float4 kk[2][R / 4], qq[2][R / 4];
       float vv[2][CV];
+      float dec[2] = {decay_h, decay_h};
 #define RET_FETCH(c, bi)                                                                        \
   {                                                                                            \
+    if (TD) dec[bi] = ds[c0 + (c)];                                                            \
     const float4* qr = reinterpret_cast<const float4*>(qs + (c0 + (c)) * dkp) + part;          \
     const float4* kr = reinterpret_cast<const float4*>(ks_ + (c0 + (c)) * dkp) + part;         \
     _Pragma("unroll") for (int r4 = 0; r4 < R / 4; ++r4) {                                     \
@@ -217,6 +234,7 @@ __global__ void __launch_bounds__(RET_THREADS) retention_scan_kernel(
 #define RET_TOKEN(c, bi)                                                                        \
   {                                                                                            \
     float a0[CV], a1[CV];                                                                      \
+    const float decay = dec[bi];                                                               \
     _Pragma("unroll") for (int j = 0; j < CV; ++j) a0[j] = a1[j] = 0.f;                        \
     _Pragma("unroll") for (int r4 = 0; r4 < R / 4; ++r4) {                                     \
       _Pragma("unroll") for (int j = 0; j < CV; ++j) {                                         \
@@ -286,6 +304,53 @@ __global__ void __launch_bounds__(RET_THREADS) retention_scan_kernel(
   }
 }
 
+static int ret_launch_scan(const float* vf, const float* qk, const float* decays,
+                           const float* tok_decay, int QH, float* state, long long state_stride,
+                           const int* q_start, const int* state_slots, int n_slots,
+                           float* o_raw, int B, int max_q, int H, int dk, int dv, int* err,
+                           cudaStream_t stream) {
+  const int R = dk <= 256 ? 8 : 32;
+  int KS = 1;
+  while (KS * R < dk) KS <<= 1;
+  // A tile of two columns a lane: half the fetches of k and q per multiply-add, half the
+  // warps.  Measured, 2,048 tokens of heads of 128 x 256, one / two / four columns a lane:
+  // 8 heads 0.52 / 0.44 / 0.79 ms, 16 heads 1.35 / 0.67 / 0.95 ms; 8 single tokens 30 / 26 /
+  // 28 us and 45 / 34 / 35 us.  Every column's sum has the same order either way.
+  const int CV = (R == 8 && dv % 2 == 0) ? 2 : 1;
+  const int cols = RET_THREADS / KS * CV;
+  dim3 grid((dv + cols - 1) / cols, H, B);
+  int stage = RET_STAGE;
+  while (stage > RET_CHUNK && stage / 2 >= max_q) stage >>= 1;
+  // (keys beyond 512 a head: fewer tokens a stage than a chunk holds; the walk takes what is there)
+  const int extra = tok_decay ? 1 : 0;      // a decay per staged token
+  while (stage > 4 && (size_t)2 * stage * (2 * KS * R + cols + extra) * sizeof(float) > 72 * 1024)
+    stage >>= 1;
+  const size_t smem = (size_t)2 * stage * (2 * KS * R + cols + extra) * sizeof(float);
+  if (smem > 200 * 1024) return (int)cudaErrorInvalidValue;
+#define RET_GO1(RR, CC, KK, TT)                                                               \
+  {                                                                                            \
+    if (smem > 48 * 1024)                                                                      \
+      cudaFuncSetAttribute(retention_scan_kernel<RR, CC, KK, TT>,                              \
+                           cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);            \
+    retention_scan_kernel<RR, CC, KK, TT><<<grid, RET_THREADS, smem, stream>>>(                \
+        vf, qk, decays, state, state_stride, q_start, state_slots, n_slots, o_raw, H, dk, dv,  \
+        KS, stage, err, tok_decay, QH);                                                        \
+  }
+#define RET_GO(RR, CC, KK)                                                                    \
+  {                                                                                            \
+    if (tok_decay) RET_GO1(RR, CC, KK, true) else RET_GO1(RR, CC, KK, false)                   \
+  }
+  if (R == 32) RET_GO(32, 1, 0)
+  else if (CV == 1) RET_GO(8, 1, 0)
+  else if (KS == 8) RET_GO(8, 2, 8)
+  else if (KS == 16) RET_GO(8, 2, 16)
+  else if (KS == 32) RET_GO(8, 2, 32)
+  else RET_GO(8, 2, 0)
+#undef RET_GO
+#undef RET_GO1
+  return bf_launch_status();
+}
+
 BF_EXPORT int bf_retention_scan(
     const void* proj, long long stride, long long q_off, long long k_off, long long v_off,
     const float* decays, const float* inv_freq, int rot_half, const int* positions, float* state,
@@ -310,40 +375,23 @@ BF_EXPORT int bf_retention_scan(
     const int e = bf_launch_status();
     if (e) return e;
   }
-  const int R = dk <= 256 ? 8 : 32;
-  int KS = 1;
-  while (KS * R < dk) KS <<= 1;
-  // A tile of two columns a lane: half the fetches of k and q per multiply-add, half the
-  // warps.  Measured, 2,048 tokens of heads of 128 x 256, one / two / four columns a lane:
-  // 8 heads 0.52 / 0.44 / 0.79 ms, 16 heads 1.35 / 0.67 / 0.95 ms; 8 single tokens 30 / 26 /
-  // 28 us and 45 / 34 / 35 us.  Every column's sum has the same order either way.
-  const int CV = (R == 8 && dv % 2 == 0) ? 2 : 1;
-  const int cols = RET_THREADS / KS * CV;
-  dim3 grid((dv + cols - 1) / cols, H, B);
-  int stage = RET_STAGE;
-  while (stage > RET_CHUNK && stage / 2 >= max_q) stage >>= 1;
-  // (keys beyond 512 a head: fewer tokens a stage than a chunk holds; the walk takes what is there)
-  while (stage > 4 && (size_t)2 * stage * (2 * KS * R + cols) * sizeof(float) > 72 * 1024)
-    stage >>= 1;
-  const size_t smem = (size_t)2 * stage * (2 * KS * R + cols) * sizeof(float);
-  if (smem > 200 * 1024) return (int)cudaErrorInvalidValue;
-#define RET_GO(RR, CC, KK)                                                                    \
-  {                                                                                            \
-    if (smem > 48 * 1024)                                                                      \
-      cudaFuncSetAttribute(retention_scan_kernel<RR, CC, KK>,                                  \
-                           cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);            \
-    retention_scan_kernel<RR, CC, KK><<<grid, RET_THREADS, smem, stream>>>(                    \
-        vf, qk, decays, state, state_stride, q_start, state_slots, n_slots, o_raw, H, dk, dv,  \
-        KS, stage, err);                                                                       \
-  }
-  if (R == 32) RET_GO(32, 1, 0)
-  else if (CV == 1) RET_GO(8, 1, 0)
-  else if (KS == 8) RET_GO(8, 2, 8)
-  else if (KS == 16) RET_GO(8, 2, 16)
-  else if (KS == 32) RET_GO(8, 2, 32)
-  else RET_GO(8, 2, 0)
-#undef RET_GO
-  return bf_launch_status();
+  return ret_launch_scan(vf, qk, decays, nullptr, H, state, state_stride, q_start, state_slots,
+                         n_slots, o_raw, B, max_q, H, dk, dv, err, stream);
+}
+
+// The scan alone, on q, k and v that are float already: qk [T][2][qk_heads][dk] (q, then k),
+// vf [T][H][dv], tok_decay [T][H].  State and output as in bf_retention_scan.
+BF_EXPORT int bf_linear_scan(const float* qk, const float* vf, const float* tok_decay,
+                             float* state, long long state_stride, const int* q_start,
+                             const int* state_slots, int n_slots, float* o_raw, int T, int B,
+                             int max_q, int H, int qk_heads, int dk, int dv, int* err,
+                             cudaStream_t stream) {
+  if (B <= 0 || T <= 0) return 0;
+  if (dk <= 0 || dv <= 0 || dk > 1024 || !qk || !vf || !tok_decay || qk_heads <= 0 ||
+      H % qk_heads)
+    return (int)cudaErrorInvalidValue;
+  return ret_launch_scan(vf, qk, nullptr, tok_decay, qk_heads, state, state_stride, q_start,
+                         state_slots, n_slots, o_raw, B, max_q, H, dk, dv, err, stream);
 }
 
 // One warp per (token, head).

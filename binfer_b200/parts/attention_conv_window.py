@@ -12,6 +12,13 @@ at their true positions) and whose softmax has a learned logit per head in its d
 the output projection.  Every key, also those of the step's own tokens, is read from the
 pages, so portions can share a step with decoded tokens.
 
+Three more things a spec may ask for: a weight behind the heads' norm (``dim`` numbers for q
+and for k that the heads share: an RMS norm with a weight per head); a learned factor per
+head on the scores, which is carried by the queries (the kernel that norms the heads
+multiplies head h's query by it, in float); and a bias per head that grows with the logarithm
+of the distance, ``b1_h ln(1 + b2_h (i - j))``, taken off the scaled score inside the attention
+kernels.
+
 The mixer can run alone (``forward``) or as a branch of ``ParallelMixers``, which stacks the
 branches' input and output projections into one product each: ``w_in`` / ``w_out`` and
 ``run(proj, ctx, view, out, out_scale)`` are that interface.
@@ -67,9 +74,15 @@ class ConvWindowAttention(Mixer):
                              "head, in halves, only")
         if spec.proj_norm and self.taps:
             raise ValueError("a norm over the whole projection goes without a convolution")
+        if spec.head_norm_weight and not spec.unit_norm:
+            raise ValueError("a weight behind the heads' norm needs that norm (unit_norm)")
+        if spec.head_norm_weight and spec.proj_norm:
+            raise ValueError("the norm over the whole projection and the weighted norm of the "
+                             "heads share their tensors' names: one of them only")
         self.names = dict(spec.names)
         self.in_rows, self.out_cols = self.channels, self.H * self.dv
         self.w_in = self.w_out = self.conv_w = self.sinks = self.proj_norm_w = None
+        self.head_w = self.temp = self.bias_slope = self.bias_rate = None
 
     # ----------------------------------------------------------------- weights
     def _spec(self, role: str) -> ParamSpec:
@@ -80,6 +93,13 @@ class ConvWindowAttention(Mixer):
         if role == "sink":
             return ParamSpec(self.prefix + self.names["sink"], (self.H,), init="around_zero",
                              role="vector")
+        if role in ("q_head_norm", "k_head_norm"):
+            return ParamSpec(self.prefix + self.names[role], (self.dk,), init="norm",
+                             role="vector")
+        if role == "temp":
+            return ParamSpec(self.prefix + self.names[role], (self.H,), init="norm", role="vector")
+        if role in ("bias_slope", "bias_rate"):
+            return ParamSpec(self.prefix + self.names[role], (self.H,), init="rate", role="vector")
         if role in ("q_norm", "k_norm"):
             return ParamSpec(self.prefix + self.names[role],
                              (self.q_size if role == "q_norm" else self.k_size,), init="norm",
@@ -96,6 +116,12 @@ class ConvWindowAttention(Mixer):
             roles.append("sink")
         if self.spec.proj_norm:
             roles += ["q_norm", "k_norm"]
+        if self.spec.head_norm_weight:
+            roles += ["q_head_norm", "k_head_norm"]
+        if self.spec.head_temperature:
+            roles.append("temp")
+        if self.spec.log_distance_bias:
+            roles += ["bias_slope", "bias_rate"]
         return roles
 
     def param_specs(self) -> List[ParamSpec]:
@@ -111,6 +137,12 @@ class ConvWindowAttention(Mixer):
             self.sinks = g("sink")
         if self.spec.proj_norm:
             self.proj_norm_w = torch.cat([g("q_norm"), g("k_norm")]).contiguous()
+        if self.spec.head_norm_weight:
+            self.head_w = torch.stack([g("q_head_norm"), g("k_head_norm")]).contiguous()
+        if self.spec.head_temperature:
+            self.temp = g("temp")
+        if self.spec.log_distance_bias:
+            self.bias_slope, self.bias_rate = g("bias_slope"), g("bias_rate")
 
     # ------------------------------------------------------------ cache, state
     def kv_need(self) -> Optional[KVNeed]:
@@ -147,10 +179,19 @@ class ConvWindowAttention(Mixer):
                         ctx.q_start, inv, ctx.positions, ctx.slots[g], q, view.k_cache,
                         view.v_cache, self.H, self.G, self.dk, self.dv, s.unit_norm, s.norm_eps,
                         ctx.err, pre_factor=factors, pre_weight=self.proj_norm_w,
-                        rot_magnitude=getattr(self.position, "magnitude", 1.0))
+                        rot_magnitude=getattr(self.position, "magnitude", 1.0),
+                        head_weight=self.head_w, q_head_scale=self.temp)
         if self.taps > 1:
             ops.conv_state_shift(proj, state, ctx.state_slots, ctx.q_start, ctx.B, self.taps)
         keep = s.keep_first if s.window is not None else 0
+        if self.bias_slope is not None:
+            ops.paged_attention_generic(
+                q, view.k_cache, view.v_cache, ctx.seq_of_token, ctx.positions,
+                ctx.block_tables[g], out, self.H, self.G, self.dk, s.window, s.softmax_scale,
+                ctx.err, sinks=self.sinks, value_dim=self.dv, keep_first=keep,
+                out_scale=out_scale, softcap=s.softcap, log_slope=self.bias_slope,
+                log_rate=self.bias_rate)
+            return
         if (DECODE_KERNEL and ctx.decode_only and s.window is None and self.sinks is None
                 and s.softmax_scale > 0 and out.stride(0) % 4 == 0 and out.data_ptr() % 8 == 0
                 and ops.decode_attention_takes_capped(q, view.k_cache, self.H, self.G, self.dk,

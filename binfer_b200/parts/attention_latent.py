@@ -14,6 +14,10 @@ token and no values.  Keys and values are never expanded.  Because ``q_h . (W_uk
 of ``rank + dr`` numbers whose first ``rank`` are also the value, and each head's result, a
 mixture of latents, is expanded by ``W_uv,h`` afterwards.  That is one path for prompt
 portions and single tokens alike, so the logits cannot depend on how a prompt was cut.
+
+With ``q_rank`` the queries go through a latent of their own: the stacked product yields
+``W_dq h`` in place of the queries, an RMS norm with a weight follows (float arithmetic), and
+a second product ``W_uq`` gives the query heads.
 """
 from __future__ import annotations
 
@@ -50,6 +54,9 @@ class LatentAttention(Mixer):
                                                        s.value_dim, s.kv_rank)
         self.q_size = self.H * (self.d + self.dr)
         self.kv_size = self.rank + self.dr
+        self.q_rank = int(getattr(s, "q_rank", 0) or 0)
+        # rows of the stacked product in front: the queries, or their latent
+        self.q_rows = self.q_rank if self.q_rank else self.q_size
         self.position = None
         if s.position is not None and self.dr:
             # the rotated sizes are a vector of their own: dr numbers, rotated from its start
@@ -57,8 +64,9 @@ class LatentAttention(Mixer):
             if self.position.inv_freq is None:
                 raise ValueError("latent attention takes rotary encodings only")
         self.names = dict(s.names)
-        self.gate_off = self.q_size + self.kv_size
+        self.gate_off = self.q_rows + self.kv_size
         self.w_proj = self.w_ukT = self.w_uv = self.w_o = self.norm_w = None
+        self.w_uq = self.q_norm_w = None
 
     # ----------------------------------------------------------------- weights
     def _spec(self, role: str) -> ParamSpec:
@@ -66,21 +74,26 @@ class LatentAttention(Mixer):
         shape = {"q": (self.q_size, self.hidden), "dkv": (self.kv_size, self.hidden),
                  "dkv_norm": (self.rank,), "uk": (self.H * self.d, self.rank),
                  "uv": (self.H * self.dv, self.rank), "g": (self.H, self.hidden),
-                 "o": (self.hidden, self.H * self.dv)}[role]
-        if role == "dkv_norm":
+                 "o": (self.hidden, self.H * self.dv), "dq": (self.q_rank, self.hidden),
+                 "dq_norm": (self.q_rank,), "uq": (self.q_size, self.q_rank)}[role]
+        if role in ("dkv_norm", "dq_norm"):
             return ParamSpec(n, shape, init="norm", role="vector")
         return ParamSpec(n, shape)
 
     def _roles(self) -> List[str]:
-        return ["q", "dkv", "dkv_norm", "uk", "uv"] + (["g"] if self.spec.head_gate else []) + ["o"]
+        q = ["dq", "dq_norm", "uq"] if self.q_rank else ["q"]
+        return q + ["dkv", "dkv_norm", "uk", "uv"] + (["g"] if self.spec.head_gate else []) + ["o"]
 
     def param_specs(self) -> List[ParamSpec]:
         return [self._spec(r) for r in self._roles()]
 
     def load(self, get: Callable[[ParamSpec], torch.Tensor]) -> None:
         g = lambda role: get(self._spec(role))          # noqa: E731
-        rows = [g("q"), g("dkv")] + ([g("g")] if self.spec.head_gate else [])
+        rows = [g("dq") if self.q_rank else g("q"), g("dkv")] + (
+            [g("g")] if self.spec.head_gate else [])
         self.w_proj = torch.cat(rows, dim=0).contiguous()
+        if self.q_rank:
+            self.w_uq, self.q_norm_w = g("uq"), g("dq_norm")
         self.norm_w = g("dkv_norm")
         # per head: W_uk,h^T [rank, d] carries a query into latent coordinates; W_uv,h
         # [dv, rank] expands a mixture of latents into the head's value
@@ -101,12 +114,18 @@ class LatentAttention(Mixer):
         proj = linear(x, self.w_proj)
         q_abs = torch.empty((T, H, self.kv_size), dtype=x.dtype, device=x.device)
         pos = self.position
-        ops.latent_encode(proj, 0, self.q_size, self.norm_w, s.norm_eps,
+        if self.q_rank:
+            c_q = torch.empty((T, self.q_rank), dtype=x.dtype, device=x.device)
+            ops.section_norm(proj, 0, self.q_rank, self.q_norm_w, s.norm_eps, c_q)
+            q = linear(c_q, self.w_uq)
+        else:
+            q = proj[:, :self.q_size]
+        ops.latent_encode(proj, 0, self.q_rows, self.norm_w, s.norm_eps,
                           pos.inv_freq if pos is not None else None,
                           bool(pos is not None and pos.interleaved),
                           pos.magnitude if pos is not None else 1.0, ctx.positions, ctx.slots[g],
-                          q_abs, view.k_cache, H, self.d, self.dr, self.rank, ctx.err)
-        q_heads = proj[:, :self.q_size].view(T, H, self.d + self.dr)
+                          q_abs, view.k_cache, H, self.d, self.dr, self.rank, ctx.err, q=q)
+        q_heads = q.view(T, H, self.d + self.dr)
         linear_heads(q_heads[:, :, :self.d], self.w_ukT, q_abs[:, :, :self.rank])
         o_lat = torch.empty((T, H, self.rank), dtype=x.dtype, device=x.device)
         if (TENSOR_CORES and s.softmax_scale > 0

@@ -28,6 +28,7 @@ from . import attention as _attention  # noqa: F401
 from . import attention_latent as _attention_latent  # noqa: F401
 from . import attention_pooled as _attention_pooled  # noqa: F401
 from . import delta_rule as _delta_rule  # noqa: F401
+from . import mamba2 as _mamba2  # noqa: F401
 from . import block as _block          # noqa: F401
 from . import block_sublayer_norm as _block_sublayer_norm  # noqa: F401
 from . import block_parallel as _block_parallel  # noqa: F401

@@ -24,14 +24,20 @@ class RMSNorm(Norm):
         self.size = size
         self.name = name
         self.env = env
+        # a weight of one number for all coordinates: held as a vector of that number, so
+        # that every kernel that takes a norm's weight takes this one too
+        self.scalar = bool(getattr(spec, "scalar_weight", False))
         self.weight: Optional[torch.Tensor] = None
 
     def param_specs(self) -> List[ParamSpec]:
         init = "around_zero" if self.offset else "norm"
-        return [ParamSpec(self.name, (self.size,), init=init, role="vector")]
+        return [ParamSpec(self.name, () if self.scalar else (self.size,), init=init,
+                          role="vector")]
 
     def load(self, get: Callable[[ParamSpec], torch.Tensor]) -> None:
         self.weight = get(self.param_specs()[0])
+        if self.scalar:
+            self.weight = self.weight.reshape(1).expand(self.size).contiguous()
         if self.offset:
             # the weight that multiplies is offset + what the checkpoint holds, in float
             self.weight = (self.weight.float() + self.offset).contiguous()

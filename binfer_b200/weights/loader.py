@@ -34,7 +34,7 @@ class ParamSpec:
     name: str
     shape: Tuple[int, ...]
     # how the random-weights mode fills it: "matrix" ~ N(0, s), "norm" ~ 1 + N(0, s_norm),
-    # "around_zero" ~ N(0, s_norm), "zeros"
+    # "around_zero" ~ N(0, s_norm), "zeros" (all of them: weights/random_init.py)
     init: str = "matrix"
     # a matrix feeds a matrix product and takes the engine's compute dtype;
     # a vector (norm weight, bias) is held in 32-bit whatever it was stored in

@@ -26,7 +26,9 @@ def random_tensor(spec: ParamSpec, seed: int, std: float, norm_std: float,
                   dtype: torch.dtype = torch.float32,
                   device: torch.device | str = "cpu") -> torch.Tensor:
     """``matrix``: N(0, std).  ``norm``: 1 + N(0, norm_std).  ``around_zero``: N(0, norm_std).
-    ``conv``: N(0, 0.5).  ``router``: N(0, 10 std).  ``zeros``: 0."""
+    ``conv``: N(0, 0.5).  ``router``: N(0, 10 std).  ``rate``: ``|N(0, 0.5)|`` (a rate or a
+    slope that must not be negative).  ``log_rate``: N(0, 0.5) - 1 (the logarithm of a decay
+    rate of order one).  ``zeros``: 0."""
     device = torch.device(device)
     g = torch.Generator(device=device)
     g.manual_seed(_tensor_seed(seed, spec.name))
@@ -47,6 +49,10 @@ def random_tensor(spec: ParamSpec, seed: int, std: float, norm_std: float,
         x.mul_(norm_std)
     elif spec.init == "conv":
         x.mul_(0.5)              # taps of a short convolution: of order one
+    elif spec.init == "rate":
+        x.abs_().mul_(0.5)
+    elif spec.init == "log_rate":
+        x.mul_(0.5).sub_(1.0)
     elif spec.init == "router":
         x.mul_(10.0 * std)       # router rows: logits far enough apart to choose by
     else:
