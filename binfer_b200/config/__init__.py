@@ -1,6 +1,6 @@
 """Configuration: architecture-neutral specs, family configs, and the architecture registry."""
 from .specs import (AttentionSpec, ConfigError, ConvWindowAttentionSpec, GatedDeltaRuleSpec,
-                    GatedMLPSpec, LatentAttentionSpec, LayerSpec, MixerBranch, MLSTMSpec,
+                    GatedMLPSpec, LatentAttentionSpec, LayerSpec, Mamba2Spec, MixerBranch, MLSTMSpec,
                     ModelSpec, MoESpec, NameLayout, NormSpec, ParallelMixersSpec, PassStart,
                     PooledWindowAttentionSpec, RampScaling, RetentionSpec, RopeSpec,
                     ScheduleEntry, ScoreSpec, WavelengthScaling)

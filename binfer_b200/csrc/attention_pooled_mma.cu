@@ -137,7 +137,8 @@ __global__ void __launch_bounds__(PWM_THREADS) pwm_attention_kernel(
     int num_pages, int s_page_size, int s_num_pages, int window, int pool, float scale_log2,
     int has_sink, float sink_log2, float* __restrict__ part_o, float* __restrict__ part_ml,
     int* __restrict__ err, const float* __restrict__ sinks, int keep_first, long long q_stride,
-    long long out_stride, float out_scale, float cap_pre, float cap_post) {
+    long long out_stride, float out_scale, float cap_pre, float cap_post,
+    const float* __restrict__ log_slope, const float* __restrict__ log_rate, float inv_scale) {
   extern __shared__ __align__(16) unsigned char smem_raw[];
   const int pitch_k = dk + 8, pitch_v = dv + 8;
   // two stages of (K tile, V tile); the first K tile's place holds the Q tile to begin with
@@ -192,6 +193,17 @@ __global__ void __launch_bounds__(PWM_THREADS) pwm_attention_kernel(
     my_j0[i] = window > 0 ? max(0, p - window + 1) : 0;
     my_nb[i] = (window > 0 && pool > 0 && p - window + 1 > 0) ? (p - window + 1) / pool : 0;
     my_kept[i] = window > 0 ? min(keep_first, my_j0[i]) : 0;   // kept tokens behind the window
+  }
+  // a bias that grows with the logarithm of the distance, of this thread's two rows' heads:
+  // slope over the scale (the scores stay unscaled until the exponent), and rate
+  float lb_slope[2] = {0.f, 0.f}, lb_rate[2] = {0.f, 0.f};
+  if (log_slope) {
+#pragma unroll
+    for (int i = 0; i < 2; ++i) {
+      const int row = min(row0 + wrow + (lane >> 2) + 8 * i, rows_total - 1);
+      lb_slope[i] = log_slope[g * Gh + row % Gh] * inv_scale;
+      lb_rate[i] = log_rate[g * Gh + row % Gh];
+    }
   }
   const int last_row = min(rows_total, row0 + PWM_ROWS) - 1;
   const int p_lo = p_first + row0 / Gh, p_hi = p_first + last_row / Gh;
@@ -289,6 +301,17 @@ __global__ void __launch_bounds__(PWM_THREADS) pwm_attention_kernel(
           float t;
           asm("ex2.approx.ftz.f32 %0, %1;" : "=f"(t) : "f"(s[n][e] * cap_pre));
           s[n][e] = cap_post - __fdividef(2.f * cap_post, t + 1.f);
+        }
+    }
+    if (log_slope && !blocks) {  // s <- s - (b1 / scale) ln(1 + b2 (p - j)), keys at their places
+#pragma unroll
+      for (int n = 0; n < PWM_KEYS / 8; ++n)
+#pragma unroll
+        for (int e = 0; e < 4; ++e) {
+          const int i = e >> 1;
+          const int kj = base + n * 8 + 2 * (lane & 3) + (e & 1);
+          const float dist = (float)max(my_p[i] - kj, 0);
+          s[n][e] -= lb_slope[i] * __logf(fmaf(lb_rate[i], dist, 1.f));
         }
     }
     // Each row masks by its own position; a tile that every row of this warp sees whole (the
@@ -592,7 +615,9 @@ BF_EXPORT int bf_pwm_attention(
     int s_page_size, int s_num_pages, int window, int pool, float scale, int has_sink,
     float sink, float* part_o, float* part_ml, int shares, int* err, const float* sinks,
     int keep_first, long long q_stride, long long out_stride, float out_scale, float softcap,
-    cudaStream_t stream) {
+    const float* log_slope, const float* log_rate, cudaStream_t stream) {
+  // log_slope, log_rate [nh] (both or neither): b1_h ln(1 + b2_h (p - j)) is taken off the
+  // scaled score of the query at p and the key at j (not with pooled blocks)
   // part_o [B, nkv, shares, 16, dv], part_ml [B, nkv, shares, 16, 2] (float, or null): scratch
   // for steps of single tokens, whose keys are then shared out over `shares` CTAs a row
   if (B <= 0 || max_tokens <= 0) return 0;
@@ -600,6 +625,8 @@ BF_EXPORT int bf_pwm_attention(
     return (int)cudaErrorInvalidValue;
   if (pool > 0 && window > 0 && !ks_cache) return (int)cudaErrorInvalidValue;
   if (!(scale > 0.f)) return (int)cudaErrorInvalidValue;     // the running maximum relies on it
+  if (!log_slope || !log_rate) log_slope = log_rate = nullptr;
+  if (log_slope && ks_cache) return (int)cudaErrorInvalidValue;
   const int Gh = nh / nkv;
   dim3 grid((max_tokens * Gh + PWM_ROWS - 1) / PWM_ROWS, nkv, B);
   const bool split = max_tokens * Gh <= 16;       // single tokens: the keys shared out over warps
@@ -626,7 +653,8 @@ BF_EXPORT int bf_pwm_attention(
       interleaved, (__nv_bfloat16*)out, nh, nkv, dk, dv, page_size, num_pages, s_page_size,
       s_num_pages, window, pool, scale * log2e, has_sink, sink * log2e, part_o, part_ml, err,
       sinks, keep_first, q_stride, out_stride, out_scale,
-      softcap > 0.f ? 2.f * log2e * scale / softcap : 0.f, softcap > 0.f ? softcap / scale : 0.f);
+      softcap > 0.f ? 2.f * log2e * scale / softcap : 0.f, softcap > 0.f ? softcap / scale : 0.f,
+      log_slope, log_rate, 1.f / scale);
   if (multi) {
     const int e = bf_launch_status();
     if (e) return e;

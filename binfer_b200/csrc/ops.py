@@ -1218,7 +1218,9 @@ def pwm_attention(q: torch.Tensor, k_cache: torch.Tensor, v_cache: torch.Tensor,
                   B: int, max_tokens: int, nh: int, nkv: int, dk: int, dv: int,
                   window: Optional[int], pool: int, scale: float, sink: Optional[float],
                   err: torch.Tensor, max_ctx: int = 0, sinks: Optional[torch.Tensor] = None,
-                  keep_first: int = 0, out_scale: float = 1.0, softcap: float = 0.0) -> None:
+                  keep_first: int = 0, out_scale: float = 1.0, softcap: float = 0.0,
+                  log_slope: Optional[torch.Tensor] = None,
+                  log_rate: Optional[torch.Tensor] = None) -> None:
     """``apw_attention`` on the tensor cores (bfloat16; sizes: ``pwm_attention_takes``):
     request ``b`` of the batch owns the token rows ``q_start[b] .. q_start[b+1]-1``, at most
     ``max_tokens`` of them.  ``max_ctx``: the longest context in the batch, if the caller
@@ -1228,7 +1230,18 @@ def pwm_attention(q: torch.Tensor, k_cache: torch.Tensor, v_cache: torch.Tensor,
     instead of the constant ``sink``.  ``keep_first``: with a window, the request's first
     that many tokens stay visible behind it.  ``out`` may be a column block of a wider
     buffer; ``out_scale`` multiplies the result.  ``softcap`` c > 0: a scaled score z becomes
-    ``c tanh(z / c)``."""
+    ``c tanh(z / c)``.  ``log_slope`` and ``log_rate`` (float32 ``[nh]`` each, together or not
+    at all; not with pooled blocks): ``log_slope_h ln(1 + log_rate_h (p - j))`` is taken off
+    the scaled score of the query at p and the key at j."""
+    if (log_slope is None) != (log_rate is None) or (log_slope is not None
+                                                     and ks_cache is not None):
+        raise KernelError("pwm_attention: log_slope and log_rate go together, without pooled "
+                          "blocks")
+    for name, t in (("log_slope", log_slope), ("log_rate", log_rate)):
+        if t is not None:
+            _want(t, torch.float32, name)
+            if t.numel() != nh:
+                raise KernelError(f"pwm_attention: {name} must have one entry per query head")
     if not pwm_attention_takes(q.dtype, nh, nkv, dk, dv):
         raise KernelError("pwm_attention: bfloat16, head sizes multiples of 16 up to 128")
     if not q.is_contiguous() or out.stride(1) != 1 or q.data_ptr() % 16:
@@ -1267,7 +1280,7 @@ def pwm_attention(q: torch.Tensor, k_cache: torch.Tensor, v_cache: torch.Tensor,
          _c_int(0 if sink is None and sinks is None else 1), _c_float(sink or 0.0),
          _ptr(part_o), _ptr(part_ml), _c_int(shares), _ptr(err), _ptr(sinks), _c_int(keep_first),
          _c_ll(q.stride(0)), _c_ll(out.stride(0)), _c_float(out_scale), _c_float(softcap),
-         _stream())
+         _ptr(log_slope), _ptr(log_rate), _stream())
 
 
 def latent_attention_takes(dtype: torch.dtype, rank: int, rot: int) -> bool:

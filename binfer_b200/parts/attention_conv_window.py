@@ -184,15 +184,8 @@ class ConvWindowAttention(Mixer):
         if self.taps > 1:
             ops.conv_state_shift(proj, state, ctx.state_slots, ctx.q_start, ctx.B, self.taps)
         keep = s.keep_first if s.window is not None else 0
-        if self.bias_slope is not None:
-            ops.paged_attention_generic(
-                q, view.k_cache, view.v_cache, ctx.seq_of_token, ctx.positions,
-                ctx.block_tables[g], out, self.H, self.G, self.dk, s.window, s.softmax_scale,
-                ctx.err, sinks=self.sinks, value_dim=self.dv, keep_first=keep,
-                out_scale=out_scale, softcap=s.softcap, log_slope=self.bias_slope,
-                log_rate=self.bias_rate)
-            return
-        if (DECODE_KERNEL and ctx.decode_only and s.window is None and self.sinks is None
+        biased = self.bias_slope is not None      # (the engine's decode and prefill kernels take none)
+        if (DECODE_KERNEL and not biased and ctx.decode_only and s.window is None and self.sinks is None
                 and s.softmax_scale > 0 and out.stride(0) % 4 == 0 and out.data_ptr() % 8 == 0
                 and ops.decode_attention_takes_capped(q, view.k_cache, self.H, self.G, self.dk,
                                                       self.dv, T)):
@@ -204,7 +197,7 @@ class ConvWindowAttention(Mixer):
                                  self.dk, None, s.softmax_scale, ctx.max_ctx_len, ctx.err,
                                  variant="persistent", softcap=s.softcap, out_scale=out_scale)
             return
-        if (DECODE_KERNEL and not ctx.decode_only and ctx.n_decode == 0 and ctx.n_prefill
+        if (DECODE_KERNEL and not biased and not ctx.decode_only and ctx.n_decode == 0 and ctx.n_prefill
                 and ctx.max_prefill_rows >= PREFILL_KERNEL_ROWS and s.window is None
                 and self.sinks is None and s.softmax_scale > 0 and out.stride(0) % 8 == 0
                 and out.data_ptr() % 16 == 0
@@ -226,12 +219,14 @@ class ConvWindowAttention(Mixer):
                               ctx.B, 1 if ctx.decode_only else ctx.max_q_len, self.H, self.G,
                               self.dk, self.dv, s.window, 0, s.softmax_scale, None, ctx.err,
                               max_ctx=ctx.max_ctx_len, sinks=self.sinks, keep_first=keep,
-                              out_scale=out_scale, softcap=s.softcap)
+                              out_scale=out_scale, softcap=s.softcap, log_slope=self.bias_slope,
+                              log_rate=self.bias_rate)
             return
         ops.paged_attention_generic(
             q, view.k_cache, view.v_cache, ctx.seq_of_token, ctx.positions, ctx.block_tables[g],
             out, self.H, self.G, self.dk, s.window, s.softmax_scale, ctx.err, sinks=self.sinks,
-            value_dim=self.dv, keep_first=keep, out_scale=out_scale, softcap=s.softcap)
+            value_dim=self.dv, keep_first=keep, out_scale=out_scale, softcap=s.softcap,
+            log_slope=self.bias_slope, log_rate=self.bias_rate)
 
 
 register_mixer("conv_window_attention", ConvWindowAttention)

@@ -579,3 +579,106 @@ def make_ketopel_dir(tmp_path, which, dtype=torch.float32, raw=None, tweak=None,
         tweak(w)
     save_file(w, os.path.join(d, "model.safetensors"))
     return d
+
+
+# ------------------------------------------------- the design with a state space layer
+def _fol_latent(heads, dim, rot_dim, vdim, rank, q_rank, base=10000.0, scale=None, dims=None):
+    return {"heads": heads, "dim": dim, "rot_dim": rot_dim, "vdim": vdim, "kv_rank": rank,
+            "q_rank": q_rank, "rot": {"base": base, "dims": rot_dim if dims is None else dims},
+            "scale": (dim + rot_dim) ** -0.5 if scale is None else scale}
+
+
+def _fol_attn(heads, kv_heads, dim, vdim, window, scale=None):
+    return {"heads": heads, "kv_heads": kv_heads, "dim": dim, "vdim": vdim,
+            "mask": {"size": window}, "scale": dim ** -0.5 if scale is None else scale}
+
+
+def _fol_mamba(heads, groups, state, vdim, conv, norm_groups):
+    return {"heads": heads, "groups": groups, "state": state, "vdim": vdim, "conv": conv,
+            "norm_groups": norm_groups}
+
+
+def _fol_moe(experts, top, ff, identity=0, groups=None, scale=1.0, shared=None):
+    router = {"experts": experts, "top": top, "identity": identity, "scale": scale}
+    if groups is not None:
+        router["groups"] = {"count": groups[0], "keep": groups[1]}
+    return {"kind": "moe", "expert": {"ff": ff}, "router": router,
+            "shared": None if shared is None else {"ff": shared}}
+
+
+def _fol_layer(kind, mixer, mlp=None):
+    return {"type": kind, "mixer": mixer, "mlp": mlp}
+
+
+# the state space layer first, two heads a group; nine router outputs in three groups, one of
+# them an identity expert; a window of 24; the last layer without a feed-forward
+FOL_A = {"architecture": "Folivik", "vocab": 300, "width": 64, "norm": {"eps": 1e-5},
+         "layers": [_fol_layer("mamba2", _fol_mamba(4, 2, 16, 24, 3, 2),
+                               _fol_moe(8, 2, 32, identity=1, groups=(3, 2), scale=1.5, shared=48)),
+                    _fol_layer("attention", _fol_attn(4, 2, 32, 16, 24, scale=0.3),
+                               _fol_moe(6, 3, 24, identity=0, groups=(2, 2), scale=0.8, shared=16)),
+                    _fol_layer("latent_attention", _fol_latent(3, 24, 8, 20, 40, 24, scale=0.2))]}
+# latent attention first; a router without groups, identity experts or a shared expert that
+# takes one expert; a state space layer without a feed-forward, a group a head, one part in
+# its norm; a window of seven, no grouping of heads, values larger than keys; two identity
+# experts among six outputs with one group of two kept; taps of four and of two
+FOL_B = {"architecture": "Folivik", "vocab": 211, "width": 48, "norm": {"eps": 1e-6},
+         "layers": [_fol_layer("latent_attention", _fol_latent(2, 16, 16, 16, 24, 16, base=500.0),
+                               _fol_moe(5, 1, 40)),
+                    _fol_layer("mamba2", _fol_mamba(3, 3, 8, 8, 4, 1)),
+                    _fol_layer("attention", _fol_attn(3, 3, 24, 40, 7),
+                               _fol_moe(4, 2, 16, identity=2, groups=(2, 1), scale=2.5, shared=56)),
+                    _fol_layer("mamba2", _fol_mamba(2, 1, 40, 12, 2, 4),
+                               _fol_moe(3, 3, 8, identity=1, groups=(1, 1), scale=1.0, shared=8))]}
+# sizes that are multiples of two only: a width of 50, a vocabulary of 131, heads of 10 and 6,
+# a state of 6; one head; a window of two; part of the rotated sizes turned; a convolution
+# of one tap
+FOL_C = {"architecture": "Folivik", "vocab": 131, "width": 50, "norm": {"eps": 1e-5},
+         "layers": [_fol_layer("attention", _fol_attn(2, 1, 10, 6, 2, scale=0.5),
+                               _fol_moe(2, 1, 6, identity=2, groups=(2, 2), scale=3.0, shared=10)),
+                    _fol_layer("mamba2", _fol_mamba(2, 1, 6, 10, 1, 5), _fol_moe(7, 2, 10, shared=4)),
+                    _fol_layer("latent_attention",
+                               _fol_latent(1, 10, 6, 6, 14, 10, base=3000.0, dims=4),
+                               _fol_moe(4, 4, 12, identity=0, groups=(4, 4), scale=0.5))]}
+# wider, for bfloat16 and the tensor-core kernels: a latent of 192 with 32 rotated sizes,
+# heads of 64 in a window of 48, a state of 64
+FOL_D = {"architecture": "Folivik", "vocab": 500, "width": 192, "norm": {"eps": 1e-5},
+         "layers": [_fol_layer("mamba2", _fol_mamba(6, 2, 64, 32, 4, 2),
+                               _fol_moe(8, 2, 128, identity=2, groups=(5, 3), scale=2.0, shared=256)),
+                    _fol_layer("latent_attention", _fol_latent(4, 64, 32, 64, 192, 96),
+                               _fol_moe(6, 2, 96, identity=0, groups=(3, 2), scale=1.0, shared=128)),
+                    _fol_layer("attention", _fol_attn(8, 4, 64, 64, 48),
+                               _fol_moe(8, 3, 64, identity=1, groups=(3, 2), scale=1.5, shared=64)),
+                    _fol_layer("mamba2", _fol_mamba(4, 4, 128, 48, 2, 1))]}
+
+FOL = {
+    "A": dict(raw=FOL_A, std=0.08, norm_std=0.1, page_size=16, seed=35),
+    "B": dict(raw=FOL_B, std=0.1, norm_std=0.1, page_size=4, seed=36),
+    "C": dict(raw=FOL_C, std=0.12, norm_std=0.1, page_size=8, seed=37),
+    "D": dict(raw=FOL_D, std=0.05, norm_std=0.05, page_size=16, seed=38),
+}
+
+
+def make_folivik_dir(tmp_path, which, dtype=torch.float32, raw=None, tweak=None, tag="") -> str:
+    """A folder with config.json and random weights of a configuration of this design;
+    ``tweak(w)`` may change the tensors (a name -> tensor dictionary) before they are written."""
+    from binfer_b200.config import FolivikConfig
+    from binfer_b200.parts.model import param_specs_for
+    from binfer_b200.weights import random_tensors, save_file
+    t = FOL[which]
+    raw = raw or t["raw"]
+    cfg = FolivikConfig.from_dict(raw)
+    d = os.path.join(str(tmp_path), f"fol_{which}{tag}_{str(dtype).split('.')[-1]}")
+    os.makedirs(d, exist_ok=True)
+    with open(os.path.join(d, "config.json"), "w") as f:
+        json.dump(cfg.to_dict(), f)
+    w = random_tensors(param_specs_for(cfg.to_spec()), t["seed"], t["std"], t["norm_std"], dtype)
+    # corrections that decide choices now and then, some of them below minus the scores
+    for n, x in w.items():
+        if n.endswith(".correction"):
+            g = torch.Generator().manual_seed(len(n) + x.numel())
+            x.copy_((torch.randn(x.shape, generator=g) * 0.15 - 0.1).to(x.dtype))
+    if tweak is not None:
+        tweak(w)
+    save_file(w, os.path.join(d, "model.safetensors"))
+    return d
