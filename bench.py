@@ -323,6 +323,36 @@ def looped_config(size, layers=8):
             "loop": {"start": 1, "stop": 3, "times": max(1, (layers - 2) // 2)}}
 
 
+def state_space_config(size, layers=8):
+    """The design with state space layers at the Qwen3 shape of that name: ``layers`` layers
+    that repeat (state space, windowed attention, state space, latent attention).  The state
+    space layer is twice as wide inside as the model, in heads of 64 with a state of 128,
+    eight groups and four taps (the sizes of the published Mamba-2 hybrids); windowed
+    attention has the shape's heads and a window of 1,024; latent attention as many heads, of
+    128 plain and 64 rotated sizes, over a latent of 512, its queries through a latent of
+    three eighths of the width; the mixture has eight experts and two identity experts in
+    five groups of which three are kept, two chosen, which with the shared expert are as many
+    active inner features as the shape's feed-forward."""
+    width, heads, kv, d, ff = HYBRID_SIZES[size][:5]
+    mlp = {"kind": "moe", "expert": {"ff": ff // 4}, "shared": {"ff": ff // 2},
+           "router": {"experts": 8, "identity": 2, "top": 2, "scale": 1.5,
+                      "groups": {"count": 5, "keep": 3}}}
+    inner = 2 * width
+    ssm = {"type": "mamba2", "mlp": mlp,
+           "mixer": {"heads": inner // 64, "vdim": 64, "state": 128, "groups": 8, "conv": 4,
+                     "norm_groups": 8}}
+    window = {"type": "attention", "mlp": mlp,
+              "mixer": {"heads": heads, "kv_heads": kv, "dim": d, "vdim": d, "scale": d ** -0.5,
+                        "mask": {"size": 1024}}}
+    latent = {"type": "latent_attention", "mlp": mlp,
+              "mixer": {"heads": heads, "dim": 128, "rot_dim": 64, "vdim": 128, "kv_rank": 512,
+                        "q_rank": 3 * width // 8, "scale": 192 ** -0.5,
+                        "rot": {"base": 1e4, "dims": 64}}}
+    pattern = [ssm, window, ssm, latent]
+    return {"architecture": "Folivik", "vocab": 32000, "width": width, "norm": {"eps": 1e-5},
+            "layers": [pattern[i % 4] for i in range(layers)]}
+
+
 def hybrid_compare(args, design="hybrid"):
     """Prefill and decode throughput of the hybrid design (matrix-memory layers alternating
     with pooled-window attention layers), or with ``design`` "side_by_side" of the design
@@ -334,15 +364,18 @@ def hybrid_compare(args, design="hybrid"):
     (event pairs around every launch, eager).  Random weights, bfloat16."""
     import torch
     from binfer_b200 import Engine, Qwen3Config
-    from binfer_b200.config import FikotarConfig, GukidraConfig, KetopelConfig
+    from binfer_b200.config import FikotarConfig, FolivikConfig, GukidraConfig, KetopelConfig
     from binfer_b200.engine.runner import StepItem
     from binfer_b200.profiling import Profiler
     layers = args.layers or 8
     B, context, ps = args.batch or 8, 4096, args.page_size
     steps, warmup = min(args.steps, 64), max(args.warmup, 3)
     what = {"hybrid": "hybrid design", "side_by_side": "side-by-side design",
-            "looped": "looped design"}[design]
-    record = {"metric": what + " beside the Qwen3 decoder at equal layer sizes "
+            "looped": "looped design", "state_space": "state space design"}[design]
+    # the design with state space layers stands beside the looped design, the closest one
+    # (latent attention, a recurrence per head, softmax attention), not beside Qwen3
+    beside = "the looped design" if design == "state_space" else "the Qwen3 decoder"
+    record = {"metric": what + " beside " + beside + " at equal layer sizes "
                         "(prefill of 2048 tokens; decode at batch %d, context %d)" % (B, context),
               "dtype": "bf16", "data": "synthetic", "layers": layers, "sizes": {}}
     for size in (args.hybrid_sizes.split(",") if args.hybrid_sizes else sorted(HYBRID_SIZES)):
@@ -352,8 +385,12 @@ def hybrid_compare(args, design="hybrid"):
         out = {}
         ours = (GukidraConfig.from_dict(hybrid_config(size, layers)) if design == "hybrid"
                 else KetopelConfig.from_dict(looped_config(size, layers)) if design == "looped"
+                else FolivikConfig.from_dict(state_space_config(size, layers))
+                if design == "state_space"
                 else FikotarConfig.from_dict(side_by_side_config(size, layers)))
-        for name, cfg in ((design, ours), ("qwen3", Qwen3Config.from_dict(qwen))):
+        other = (("looped", KetopelConfig.from_dict(looped_config(size, layers)))
+                 if design == "state_space" else ("qwen3", Qwen3Config.from_dict(qwen)))
+        for name, cfg in ((design, ours), other):
             engine = Engine(cfg, "bfloat16", random_seed=0, num_pages=(B + 1) * (context // ps) + 64,
                             page_size=ps, max_seq_len=context, max_batch_size=B + 1,
                             max_tokens_per_step=2048, cuda_graphs=True)
@@ -498,8 +535,13 @@ def main():
                     help="the same for the design whose layers (latent attention, the gated "
                          "delta rule, whole-norm attention beside lightning attention) are "
                          "partly walked several times")
-    ap.add_argument("--hybrid-sizes", default="", help="with --hybrid, --side-by-side or --looped: 1.7b, "
-                                                       "8b or both (default)")
+    ap.add_argument("--state-space", action="store_true",
+                    help="the same for the design with state space layers (Mamba-2), windowed "
+                         "attention with a logarithmic distance bias and latent attention, with "
+                         "a grouped router over experts and identity experts; it stands beside "
+                         "the looped design instead of Qwen3")
+    ap.add_argument("--hybrid-sizes", default="", help="with --hybrid, --side-by-side, --looped or "
+                                                       "--state-space: 1.7b, 8b or both (default)")
     args = ap.parse_args()
     if args.impl == "reference":
         return reference_arm()
@@ -514,6 +556,8 @@ def main():
         return hybrid_compare(args, "side_by_side")
     if args.looped:
         return hybrid_compare(args, "looped")
+    if args.state_space:
+        return hybrid_compare(args, "state_space")
     if args.profile:
         return profile_steps(args)
     if args.workload == "serve":

@@ -359,11 +359,41 @@ __global__ void moe_identity_add_kernel(A* __restrict__ out, const A* __restrict
   if (wgt != 0.f) bf_st(out + i, bf_ld(out + i) + wgt * bf_ld(h + (size_t)t * stride + c));
 }
 
+// bfloat16, a width that is a multiple of 8 and rows on 16-byte boundaries: eight columns a thread
+__global__ void moe_identity_add_bf16_vec_kernel(__nv_bfloat16* __restrict__ out,
+                                                 const __nv_bfloat16* __restrict__ h,
+                                                 long long stride,
+                                                 const float* __restrict__ route_w, int rw_cols,
+                                                 int col, int T, int width) {
+  const long long i = (long long)blockIdx.x * blockDim.x + threadIdx.x;
+  const int w8 = width >> 3;
+  if (i >= (long long)T * w8) return;
+  const int t = (int)(i / w8), c = (int)(i % w8) << 3;
+  const float wgt = route_w[(size_t)t * rw_cols + col];
+  if (wgt == 0.f) return;
+  uint4 o4 = *reinterpret_cast<const uint4*>(out + (size_t)t * width + c);
+  const uint4 h4 = *reinterpret_cast<const uint4*>(h + (size_t)t * stride + c);
+  __nv_bfloat162* o2 = reinterpret_cast<__nv_bfloat162*>(&o4);
+  const __nv_bfloat162* h2 = reinterpret_cast<const __nv_bfloat162*>(&h4);
+#pragma unroll
+  for (int j = 0; j < 4; ++j) {
+    const float2 a = __bfloat1622float2(o2[j]), b = __bfloat1622float2(h2[j]);
+    o2[j] = __floats2bfloat162_rn(a.x + wgt * b.x, a.y + wgt * b.y);
+  }
+  *reinterpret_cast<uint4*>(out + (size_t)t * width + c) = o4;
+}
+
 BF_EXPORT int bf_moe_identity_add(void* out, const void* h, long long stride,
                                   const float* route_w, int rw_cols, int col, int T, int width,
                                   int act_dtype, cudaStream_t stream) {
   if (T <= 0 || width <= 0) return 0;
   const long long n = (long long)T * width;
+  if (act_dtype == BF_DTYPE_BF16 && width % 8 == 0 && stride % 8 == 0 &&
+      (((uintptr_t)out | (uintptr_t)h) & 15) == 0) {
+    moe_identity_add_bf16_vec_kernel<<<(unsigned)((n / 8 + 255) / 256), 256, 0, stream>>>(
+        (__nv_bfloat16*)out, (const __nv_bfloat16*)h, stride, route_w, rw_cols, col, T, width);
+    return bf_launch_status();
+  }
   const unsigned blocks = (unsigned)((n + 255) / 256);
   if (act_dtype == BF_DTYPE_F32)
     moe_identity_add_kernel<float><<<blocks, 256, 0, stream>>>(

@@ -323,18 +323,43 @@ static int ret_launch_scan(const float* vf, const float* qk, const float* decays
   while (stage > RET_CHUNK && stage / 2 >= max_q) stage >>= 1;
   // (keys beyond 512 a head: fewer tokens a stage than a chunk holds; the walk takes what is there)
   const int extra = tok_decay ? 1 : 0;      // a decay per staged token
-  while (stage > 4 && (size_t)2 * stage * (2 * KS * R + cols + extra) * sizeof(float) > 72 * 1024)
-    stage >>= 1;
-  const size_t smem = (size_t)2 * stage * (2 * KS * R + cols + extra) * sizeof(float);
-  if (smem > 200 * 1024) return (int)cudaErrorInvalidValue;
+  const size_t per_token = (size_t)2 * (2 * KS * R + cols + extra) * sizeof(float);
+  while (stage > 4 && stage * per_token > 72 * 1024) stage >>= 1;
+  if (stage * per_token > 200 * 1024) return (int)cudaErrorInvalidValue;
+  // More blocks than SMs: of the staging depths from this one down to a chunk, take the one
+  // whose resident blocks walk the grid in the fewest waves (a grid a little larger than what
+  // is resident at once runs twice as long), the deepest of those.  No sum's order depends on it.
+  static int n_sms[BF_MAX_DEVICES];
+  const int dev = bf_current_device();
+  if (!n_sms[dev]) {
+    int n = 0;
+    cudaDeviceGetAttribute(&n, cudaDevAttrMultiProcessorCount, dev);
+    n_sms[dev] = n > 0 ? n : 148;
+  }
+  const long long blocks_total = (long long)grid.x * grid.y * grid.z;
 #define RET_GO1(RR, CC, KK, TT)                                                               \
   {                                                                                            \
-    if (smem > 48 * 1024)                                                                      \
-      cudaFuncSetAttribute(retention_scan_kernel<RR, CC, KK, TT>,                              \
-                           cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);            \
-    retention_scan_kernel<RR, CC, KK, TT><<<grid, RET_THREADS, smem, stream>>>(                \
+    auto kern = retention_scan_kernel<RR, CC, KK, TT>;                                         \
+    int st = stage;                                                                            \
+    if (stage * per_token > 48 * 1024)                                                         \
+      cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize,                  \
+                           (int)(stage * per_token));                                          \
+    if (blocks_total > n_sms[dev]) {                                                           \
+      long long best = -1;                                                                     \
+      for (int c = stage; c >= RET_CHUNK; c >>= 1) {                                           \
+        int nb = 0;                                                                            \
+        if (cudaOccupancyMaxActiveBlocksPerMultiprocessor(&nb, kern, RET_THREADS,              \
+                                                          c * per_token) != cudaSuccess ||    \
+            nb < 1)                                                                            \
+          continue;                                                                            \
+        const long long at_once = (long long)n_sms[dev] * nb;                                  \
+        const long long waves = (blocks_total + at_once - 1) / at_once;                        \
+        if (best < 0 || waves < best) { best = waves; st = c; }                                \
+      }                                                                                        \
+    }                                                                                          \
+    kern<<<grid, RET_THREADS, st * per_token, stream>>>(                                       \
         vf, qk, decays, state, state_stride, q_start, state_slots, n_slots, o_raw, H, dk, dv,  \
-        KS, stage, err, tok_decay, QH);                                                        \
+        KS, st, err, tok_decay, QH);                                                           \
   }
 #define RET_GO(RR, CC, KK)                                                                    \
   {                                                                                            \

@@ -216,6 +216,54 @@ def add_rmsnorm(a):
     report("add_rmsnorm", us, nbytes=T * H * (4 + 4 + 2 + 2), tokens=T, hidden=H)
 
 
+FP32_TFLOPS_NOMINAL = 148 * 128 * 2 * 1.965e9 / 1e12      # FMA lanes x 2 x the largest SM clock
+
+
+def scan(a):
+    """A recurrence over --tokens tokens of --batch requests, alone: ``linear`` (a decay per
+    token and head, q and k shared by groups of heads: the state space layer's), ``delta``
+    (the gated delta rule) or ``retention`` (a fixed decay per head), --heads heads with
+    --kv-heads heads of q and k, keys (the state's first size) of --state and values of
+    --head-dim.  Arithmetic is counted as the recurrence's own multiply-adds (state update and
+    read-out: 5 flops a state element and token, the delta rule 9) against the nominal float
+    rate of the FMA pipes; there is no measured peak for it."""
+    dev = torch.device("cuda:0")
+    B, n, H, G, N, P = a.batch, a.tokens, a.heads, a.kv_heads, a.state, a.head_dim
+    T = B * n
+    err = ops.error_word(dev)
+    q_start = torch.arange(0, T + 1, n, device=dev, dtype=torch.int32)
+    slots = torch.arange(B, device=dev, dtype=torch.int32)
+    state = torch.zeros(B + 1, H * N * P, device=dev)
+    o = torch.empty(T, H * P, device=dev)
+    sets = []
+    for _ in range(2):
+        if a.kind == "linear":
+            qk = torch.randn(T, 2, G, N, device=dev) * 0.1
+            vf = torch.randn(T, H, P, device=dev)
+            dec = torch.rand(T, H, device=dev) * 0.2 + 0.8
+            sets.append(lambda qk=qk, vf=vf, dec=dec: ops.linear_scan(
+                qk, vf, dec, state, q_start, slots, o, B, H, G, N, P, err, max_q=n))
+        elif a.kind == "delta":
+            qkv = torch.randn(T, 2 * G * N + H * P, device=dev) * 0.1
+            gates = torch.rand(T, 2, H, device=dev) * 0.2 + 0.8
+            sets.append(lambda qkv=qkv, gates=gates: ops.delta_scan(
+                qkv, gates, state, q_start, slots, o, B, H, G, N, P, err, max_q=n))
+        else:
+            proj = (torch.randn(T, H * (2 * N + P), device=dev) * 0.1).to(BF16)
+            dec = torch.rand(H, device=dev) * 0.2 + 0.8
+            pos = torch.arange(n, device=dev, dtype=torch.int32).repeat(B)
+            sets.append(lambda proj=proj, dec=dec, pos=pos: ops.retention_scan(
+                proj, 0, H * N, 2 * H * N, dec, None, pos, state, q_start, slots, o, B, H, N, P,
+                1.0, err, max_q=n))
+    us = timed(sets, a.iters, a.warmup)
+    flops = (9.0 if a.kind == "delta" else 5.0) * T * H * N * P
+    out = {"kernel": a.kind + "_scan", "us": round(us, 2), "tokens": n, "requests": B, "heads": H,
+           "qk_heads": G, "keys": N, "values": P, "TFLOP/s": round(flops / us / 1e6, 2),
+           "frac_of_nominal_fp32": round(flops / us / 1e6 / FP32_TFLOPS_NOMINAL, 3)}
+    print(json.dumps(out), flush=True)
+    assert int(err.item()) == 0
+
+
 def step_timeline(a):
     import ctypes
     from . import Engine
@@ -287,7 +335,7 @@ def main(argv=None):
     ap = argparse.ArgumentParser(prog="python -m binfer_b200.microbench", description=__doc__,
                                  formatter_class=argparse.RawDescriptionHelpFormatter)
     ap.add_argument("kernel", choices=["decode_attention", "prefill_attention", "gemm",
-                                       "swiglu", "add_rmsnorm", "step_timeline"])
+                                       "swiglu", "add_rmsnorm", "step_timeline", "scan"])
     ap.add_argument("--iters", type=int, default=50)
     ap.add_argument("--warmup", type=int, default=5)
     ap.add_argument("--batch", type=int, default=8)
@@ -301,6 +349,9 @@ def main(argv=None):
     ap.add_argument("--scattered", action="store_true",
                     help="decode_attention: no two pages of a tile side by side in the pool")
     ap.add_argument("--hidden", type=int, default=4096)
+    ap.add_argument("--kind", default="linear", choices=["linear", "delta", "retention"],
+                    help="scan: which recurrence")
+    ap.add_argument("--state", type=int, default=128, help="scan: size of a key (the state's rows)")
     ap.add_argument("--layers", type=int, default=6, help="step_timeline: layers of the model")
     ap.add_argument("--intermediate", type=int, default=12288)
     ap.add_argument("--vocab", type=int, default=151936)
@@ -328,7 +379,7 @@ def main(argv=None):
     GRAPH = not a.no_graph
     {"decode_attention": decode_attention, "prefill_attention": prefill_attention,
      "gemm": gemm, "swiglu": swiglu, "add_rmsnorm": add_rmsnorm,
-     "step_timeline": step_timeline}[a.kernel](a)
+     "step_timeline": step_timeline, "scan": scan}[a.kernel](a)
     return 0
 
 
