@@ -196,7 +196,7 @@ def test_mixture_of_experts_alone(cuda_device, dtype, mlp, width):
 
 @pytest.mark.parametrize("H_,G_,N,P_", [(4, 2, 16, 24), (3, 3, 8, 8), (2, 1, 40, 12), (2, 1, 6, 10),
                                         (6, 2, 64, 32), (1, 1, 128, 64), (2, 2, 300, 4),
-                                        (1, 1, 1, 1)])
+                                        (1, 1, 1, 1), (3, 1, 10, 7), (2, 2, 33, 5)])
 def test_scan_with_a_decay_per_token(cuda_device, H_, G_, N, P_):
     """The recurrence alone: unequal requests in one launch, states that continue from slots
     in a shuffled order, against the recurrence written out token by token."""
@@ -237,7 +237,7 @@ def test_scan_with_a_decay_per_token(cuda_device, H_, G_, N, P_):
 # ------------------------------------------------------------------ mechanisms alone
 @pytest.mark.parametrize("heads,groups,state,vdim,conv,parts", [
     (4, 2, 16, 24, 3, 2), (3, 3, 8, 8, 4, 1), (2, 1, 40, 12, 2, 4), (2, 1, 6, 10, 1, 5),
-    (1, 1, 128, 64, 4, 1), (6, 3, 72, 20, 5, 3), (2, 2, 320, 6, 2, 2)])
+    (1, 1, 128, 64, 4, 1), (6, 3, 72, 20, 5, 3), (2, 2, 320, 6, 2, 2), (3, 1, 10, 7, 3, 3)])
 def test_state_space_layer_alone(cuda_device, tmp_path, heads, groups, state, vdim, conv, parts):
     """One layer: a prompt at once, portions, and token by token, over 200 tokens, with a
     decay close to one on the first head, so that the first tokens still count at the end."""
