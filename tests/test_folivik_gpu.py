@@ -489,6 +489,38 @@ def test_windowed_attention_at_its_edges_on_the_tensor_cores(cuda_device, tmp_pa
         assert worst <= 0.03, f"{case}/{name}: the two kernels differ by {worst:.3g}"
 
 
+@pytest.mark.parametrize("window", [1, 2, 7, 64, 65, 500])
+def test_windows_small_and_large_on_the_tensor_cores(cuda_device, tmp_path, window):
+    """Windows of one token (a query sees itself alone), of less than a key tile, of exactly a
+    tile and one more, and wider than the sequence, in bfloat16 on the tiled kernel and on the
+    kernel for any sizes: both within rounding of the plain implementation and of each other."""
+    from binfer_b200.parts import attention_conv_window as mod
+    raw = _one_layer(H._fol_layer("attention", H._fol_attn(4, 2, 32, 16, window, scale=0.4),
+                                  SMALL_MOE), vocab=300, width=64)
+    d = H.make_folivik_dir(tmp_path, "D", torch.bfloat16, raw=raw, tag=f"w{window}")
+    raw, w = H.read_model_dir(d)
+    reqs = {"a": H.random_tokens(150, raw["vocab"], 5), "b": H.random_tokens(66, raw["vocab"], 6)}
+    ref = {r: P.forward(raw, w, t) for r, t in reqs.items()}
+    if window < 150:
+        off = copy.deepcopy(raw)
+        off["layers"][0]["mixer"]["mask"]["size"] = window + 1
+        assert H.rel_err(P.forward(off, w, reqs["a"]), ref["a"]) > 1e-2
+    outs = []
+    for on in (True, False):
+        mod.TENSOR_CORES = on
+        try:
+            got = {}
+            for name, steps in _all_regimes(reqs, tail=70).items():
+                got[name] = H.run_trace(_runner(d, torch.bfloat16, 8, H.peak_pages(steps, 8)), steps)
+                _compare(got[name], ref, torch.bfloat16, f"window {window}/{name} (tensor cores {on})")
+        finally:
+            mod.TENSOR_CORES = True
+        outs.append(got)
+    for name in outs[0]:
+        worst = max(H.rel_err(outs[0][name][k], outs[1][name][k]) for k in outs[0][name])
+        assert worst <= 0.05, f"window {window}/{name}: the two kernels differ by {worst:.3g}"
+
+
 # ----------------------------------------------------------------------- whole models
 LENGTHS = {"A": [5, 17, 33, 70, 121], "B": [1, 9, 40, 70, 101], "C": [3, 30, 64, 47, 2],
            "D": [2, 45, 150, 210, 90]}
